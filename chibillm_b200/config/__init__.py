@@ -1,8 +1,8 @@
 """Configuration: typed reading of config.json and the architecture registry."""
 from .base import ConfigError, KeyReader, read_config_json
-from .spec import (AdapterSpec, AttentionSpec, DeltaRuleSpec, DenseMLPSpec, FeedForwardSpec, GatedMLPSpec, LayerSpec,
-                   MixerSpec, ModelSpec, NormSpec, PositionSpec, RunStep, ShortConvSpec, TableExpertsSpec,
-                   TokenInputSpec)
+from .spec import (AdapterSpec, AttentionSpec, DeltaRuleSpec, DenseMLPSpec, FeedForwardSpec, GatedMLPSpec,
+                   GatedRecurrenceSpec, LatentAttentionSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                   RoutedExpertsSpec, RunStep, ShortConvSpec, TableExpertsSpec, TokenInputSpec)
 from .registry import (Architecture, find_architecture, load_config, register_architecture,
                        registered_architectures, unregister_architecture)
 from .qwen3 import ARCHITECTURE as QWEN3_ARCHITECTURE, MODEL_TYPE as QWEN3_MODEL_TYPE, Qwen3Config
@@ -16,12 +16,16 @@ register_architecture(GITIPEL_ARCHITECTURE, GitipelConfig.from_dict, GitipelConf
 from .fokurax import ARCHITECTURE as FOKURAX_ARCHITECTURE, FokuraxConfig
 
 register_architecture(FOKURAX_ARCHITECTURE, FokuraxConfig.from_dict, FokuraxConfig.model_spec, replace=True)
+from .pitudra import ARCHITECTURE as PITUDRA_ARCHITECTURE, PitudraConfig
+
+register_architecture(PITUDRA_ARCHITECTURE, PitudraConfig.from_dict, PitudraConfig.model_spec, replace=True)
 
 __all__ = [
     "ConfigError", "KeyReader", "read_config_json",
     "AdapterSpec", "AttentionSpec", "FeedForwardSpec", "GatedMLPSpec", "LayerSpec", "MixerSpec", "ModelSpec",
     "NormSpec", "PositionSpec", "RunStep", "DeltaRuleSpec", "DenseMLPSpec", "ShortConvSpec", "GitipelConfig",
-    "TableExpertsSpec", "TokenInputSpec", "FokuraxConfig",
+    "TableExpertsSpec", "TokenInputSpec", "FokuraxConfig", "GatedRecurrenceSpec", "LatentAttentionSpec",
+    "RoutedExpertsSpec", "PitudraConfig",
     "Architecture", "find_architecture", "load_config", "register_architecture",
     "registered_architectures", "unregister_architecture", "Qwen3Config",
 ]

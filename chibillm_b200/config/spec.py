@@ -18,15 +18,18 @@ from typing import Optional, Tuple
 class NormSpec:
     """A normalisation over the last ``size`` features.
 
-    ``kind`` names a registered norm part ("rmsnorm").  ``weight_offset`` is
-    added to the stored weight before use (0 for plain RMSNorm, 1 for the
-    zero-centred variant).
+    ``kind`` names a registered norm part ("rmsnorm"; "layernorm": the mean is
+    taken off first, the variance is the mean of the squared deviations, and a
+    bias, the tensor of the weight's name with ``bias_suffix`` added, follows the
+    weight).  ``weight_offset`` is added to the stored weight before use (0 for
+    plain RMSNorm, 1 for the zero-centred variant).
     """
 
     kind: str
     size: int
     eps: float
     weight_offset: float = 0.0
+    bias_suffix: str = ".b"
 
 
 @dataclass(frozen=True)
@@ -84,6 +87,16 @@ class AttentionSpec(MixerSpec):
     weight; ``qk_norm`` by contrast comes before the rotation and has weights.
     ``own_kv`` False: the layer has no key and value projections at all and runs
     only as a reader of another run step's cache (``RunStep.cache_of``).
+    ``sink``: a learned number per query head (tensor role "sink") joins the
+    softmax's denominator as exp(sink), unscaled, without a key or a value.
+    ``biases``: the q, k and v projections add a vector each (roles "q_bias",
+    "k_bias", "v_bias").  ``whole_norm_eps`` (None: off): q and k are divided by
+    the root mean square of their WHOLE projection (all heads at once, this eps
+    inside the root) and multiplied by weights of that size (roles "q_norm",
+    "k_norm"), before any rotation.  ``output_gate``: the concatenated heads are
+    multiplied by sigmoid(Wg x) (role "g_proj") before the output projection.
+    ``cache_window``: how long the cache keeps a key where that is not ``window``
+    (a layer whose cache a layer with a longer window reads); "same" = ``window``.
     """
 
     hidden_size: int = 0
@@ -101,6 +114,65 @@ class AttentionSpec(MixerSpec):
     chunk: Optional[int] = None
     unit_norm_eps: Optional[float] = None
     own_kv: bool = True
+    sink: bool = False
+    biases: bool = False
+    whole_norm_eps: Optional[float] = None
+    output_gate: bool = False
+    cache_window: object = "same"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Attention whose keys and values are made from one cached latent per token.
+
+    c_q = RMSNorm(W_dq x) (``q_rank`` features, weight role "q_latent_norm"),
+    q = W_uq c_q: per head ``head_dim`` plain features followed by ``rope_dim``
+    rotated ones.  W_dkv x has ``kv_rank`` + ``rope_dim`` rows: the first,
+    RMS-normalised (role "kv_latent_norm"), are the latent c; the last, rotated,
+    are one key part that all heads share.  Head h's plain key is W_uk[h] c, its
+    value W_uv[h] c (``value_dim`` features); score = (q_plain . k_plain +
+    q_rot . k_rot) * ``scale``.  The cache holds c and the rotated part only
+    (one row of ``kv_rank`` + ``rope_dim`` numbers per token).  ``window``,
+    ``sink``, ``own_kv`` and ``cache_window`` as for AttentionSpec (a layer
+    without W_dkv reads another step's cache with W_uk and W_uv of its own).
+    ``position`` rotates the ``rope_dim`` part (its ``head_dim`` is ``rope_dim``).
+    """
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    rope_dim: int = 0
+    value_dim: int = 0
+    q_rank: int = 0
+    kv_rank: int = 0
+    scale: float = 0.0
+    norm_eps: float = 0.0
+    window: Optional[int] = None
+    sink: bool = False
+    own_kv: bool = True
+    position: PositionSpec = PositionSpec(kind="none")
+    cache_window: object = "same"
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec(MixerSpec):
+    """Linear attention whose forget gate also sets what is written: per head a
+    state S [``head_dim``, ``value_dim``] (32-bit, zero at a sequence's start),
+
+        q = silu(Wq x),  v = Wv x,  f = l + (1 - l) * sigmoid(Wf x + bf)
+        S <- diag(f) S + (1 - f) v^T,   o = S^T q
+
+    with a lower bound l per gate channel (role "gate_floor").  Each head's o is
+    divided by its root mean square (``norm_eps`` inside the root) and multiplied by
+    a weight of ``value_dim`` numbers that the heads share (role "out_norm"), then
+    projected back to ``hidden_size``.
+    """
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    norm_eps: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -175,6 +247,22 @@ class TableExpertsSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class RoutedExpertsSpec(FeedForwardSpec):
+    """``num_experts`` small feed-forwards without gate or biases, down(act(up(x))),
+    of which every token uses ``top``: those with the largest router logits
+    (z = W_router x in 32-bit; role "router"), weighted by the softmax over the
+    chosen logits only.  ``activation``: "relu2" (the square of relu), "relu",
+    "silu", "gelu" or "gelu_tanh".  Tensor roles of expert e: "expert_up",
+    "expert_down", each a name with ``{e}`` where the number goes."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    num_experts: int = 0
+    top: int = 0
+    activation: str = "relu2"
+
+
+@dataclass(frozen=True)
 class TokenInputSpec:
     """A per-layer input from the token's id at the end of a block.  A table shared
     by all layers (``table_name`` [vocab_size, table_width]) holds ``dim`` features
@@ -208,7 +296,11 @@ class LayerSpec:
     """One block: how mixer, feed-forward and norms are arranged.
 
     ``arrangement`` names a registered block ("prenorm": x + mixer(norm(x)),
-    then x + ff(norm(x))).  ``weight_prefix`` is the checkpoint prefix of the
+    then x + ff(norm(x)); "postnorm": the norms sit on the sublayers' outputs,
+    x + norm(mixer(x)), then x + norm(ff(x))).  ``token_shift`` (arrangement
+    "postnorm"): the mixer reads h + (h' - h) * w with h' the token before (zeros
+    before the first; tensor role "token_shift"), and the last h is part of a
+    request's state.  ``weight_prefix`` is the checkpoint prefix of the
     block's tensors.  ``weight_names`` maps the part-local tensor roles to
     checkpoint names under that prefix.  ``feed_forward`` (with its norm) may be
     None: the block then ends after the mixer.  ``mixer_conv``: a short
@@ -227,6 +319,7 @@ class LayerSpec:
     # arrangement "parallel": one norm, x += residual_scale * (mixer(norm(x)) + ff(norm(x)))
     residual_scale: float = 1.0
     token_input: Optional[TokenInputSpec] = None
+    token_shift: bool = False
 
     def names(self) -> dict:
         return dict(self.weight_names)

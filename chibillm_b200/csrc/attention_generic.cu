@@ -17,6 +17,8 @@
 //
 // Options of the score: a soft cap c (0 = off) replaces s by c * tanh(s / c); a bias by
 // distance (r1, r2 per query head, null = off) then takes r1 * ln(1 + r2 * (pos - key)) off.
+// A sink (one number per query head, null = off) joins the softmax's denominator as exp(sink): the
+// running maximum starts at the sink and the running sum at one, with nothing accumulated for it.
 #define CHIBI_UNIT attention_generic
 #define CHIBI_UNIT_ID 4
 #include "common.cuh"
@@ -35,7 +37,8 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                          const int* __restrict__ positions,
                          long long tokens, int nq, int nkv, int d, int dv, int page_size, int num_pages,
                          float scale, int window, int chunk, float softcap, const float* __restrict__ bias_r1,
-                         const float* __restrict__ bias_r2, int* __restrict__ error)
+                         const float* __restrict__ bias_r2, const float* __restrict__ sink,
+                         int* __restrict__ error)
 {
     pdl_enter();
     extern __shared__ float smem[];
@@ -63,6 +66,10 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
     for (int i = 0; i < SLOTS; ++i)
         acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
+    if (sink) {
+        m = sink[head];
+        l = 1.f;
+    }
 
     for (int base = first; base <= pos; base += 32) {
         const int u = base + lane;
@@ -132,8 +139,8 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
                                       const int* positions,
                                       long long tokens, int nq, int nkv, int d, int dv, int page_size,
                                       int num_pages, float scale, int window, int chunk, float softcap,
-                                      const float* bias_r1, const float* bias_r2, int* error,
-                                      cudaStream_t stream)
+                                      const float* bias_r1, const float* bias_r2, const float* sink,
+                                      int* error, cudaStream_t stream)
 {
     if (tokens <= 0)
         return CHIBI_OK;
@@ -149,7 +156,7 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
         launch(attention_generic_kernel<TQ, TC>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 
             (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
             table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, dv, page_size,
-            num_pages, scale, window, chunk, softcap, bias_r1, bias_r2, error);
+            num_pages, scale, window, chunk, softcap, bias_r1, bias_r2, sink, error);
     }));
     return launch_status();
 }

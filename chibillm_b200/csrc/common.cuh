@@ -45,7 +45,7 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
     return __float2bfloat16_rn(v);
 }
 
-// Activations by code, in 32-bit: 0 gelu with erf, 1 gelu with tanh, 2 silu, 3 relu, 4 tanh.
+// Activations by code, in 32-bit: 0 gelu with erf, 1 gelu with tanh, 2 silu, 3 relu, 4 tanh, 5 the square of relu.
 __device__ __forceinline__ float activate(float z, int kind)
 {
     switch (kind) {
@@ -53,6 +53,7 @@ __device__ __forceinline__ float activate(float z, int kind)
     case 1: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
     case 2: return z / (1.f + expf(-z));
     case 4: return tanhf(z);
+    case 5: { const float r = fmaxf(z, 0.f); return r * r; }
     default: return fmaxf(z, 0.f);
     }
 }

@@ -178,7 +178,8 @@ __global__ void gated_activation_vec8_kernel(const __nv_bfloat16* __restrict__ g
 // offsets[experts + 1], pair_of_row[pairs] (rows sorted by expert), row_of_pair[pairs],
 // the tile map: tile_expert[max_tiles] (-1: unused), tile_row0[max_tiles], every tile
 // holding up to tile_rows rows of one expert (max_tiles = ceil(pairs / tile_rows) + experts),
-// and token_of_row[pairs] (which row of the tokens' array every sorted row reads).
+// and token_of_row[pairs] (which row of the tokens' array every sorted row reads).  Without `tokens` the
+// table has a row per token of the step (a router's choices) instead of one per token id.
 __global__ void __launch_bounds__(1024)
 route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int vocab, int top, int experts,
                       int num_tokens, int tile_rows, int max_tiles, int* __restrict__ offsets,
@@ -193,7 +194,7 @@ route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ ta
         counts[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int tok = tokens[p / top];
+        const int tok = tokens ? tokens[p / top] : p / top;
         int e = (tok >= 0 && tok < vocab) ? table[(size_t)tok * top + p % top] : -1;
         if (e < 0 || e >= experts) {
             if (error)
@@ -225,7 +226,7 @@ route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ ta
     // Where a row lands within its expert's range depends on the order in which the threads arrive;
     // every row is computed by itself and found again through row_of_pair, so no value depends on it.
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int tok = tokens[p / top];
+        const int tok = tokens ? tokens[p / top] : p / top;
         int e = (tok >= 0 && tok < vocab) ? table[(size_t)tok * top + p % top] : 0;
         if (e < 0 || e >= experts)
             e = 0;
@@ -238,7 +239,8 @@ route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ ta
 
 // Tiles of EG_M rows of one expert times 64 columns; 256 threads, a thread owns 4 x 4 sums.
 // out[r, n] = sum_k a[row(r), k] * w[expert][n, k]; GATED: w[expert] holds 2 N rows (gate rows,
-// then up rows) and out[r, n] = act(gate sum) * (up sum).  row(r) = a_index[r] / a_div when
+// then up rows) and out[r, n] = act(gate sum) * (up sum); not GATED with kind >= 0: out = act(sum).
+// row(r) = a_index[r] / a_div when
 // a_index is given (the rows of the tokens' array that the sorted pairs point at), else r.
 // The K range is walked in order, so a row's sums do not depend on what shares its tile.
 constexpr int EG_M = 64, EG_N = 64, EG_K = 16;
@@ -324,6 +326,8 @@ expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int*
             float v = acc[0][i][j];
             if (GATED)
                 v = activate(v, kind) * acc[GATED ? 1 : 0][i][j];
+            else if (kind >= 0)
+                v = activate(v, kind);
             out[(size_t)r * out_stride + n] = from_f32<TO>(v);
         }
     }
@@ -496,10 +500,11 @@ expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, 
     }
 }
 
-// acc[t, c] += weight * sum over the token's choices (in their order) of y[row_of_pair[t * top + s], c]
+// acc[t, c] += weight * sum over the token's choices (in their order) of y[row_of_pair[t * top + s], c],
+// each times pair_weight[t * top + s] where that is given
 __global__ void combine_experts_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
                                        float* __restrict__ acc, long long acc_stride, long long tokens, int n, int top,
-                                       float weight)
+                                       float weight, const float* __restrict__ pair_weight)
 {
     pdl_enter();
     const long long total = tokens * n;
@@ -508,8 +513,10 @@ __global__ void combine_experts_kernel(const float* __restrict__ y, const int* _
         const long long t = i / n;
         const int c = (int)(i - t * n);
         float s = 0.f;
-        for (int k = 0; k < top; ++k)
-            s += y[(size_t)row_of_pair[t * top + k] * n + c];
+        for (int k = 0; k < top; ++k) {
+            const float v = y[(size_t)row_of_pair[t * top + k] * n + c];
+            s = pair_weight ? fmaf(pair_weight[t * top + k], v, s) : s + v;
+        }
         acc[t * acc_stride + c] += weight * s;
     }
 }
@@ -719,7 +726,7 @@ CHIBI_API int chibi_route_by_table(const int* tokens, const int* table, int voca
 {
     if (num_tokens <= 0)
         return CHIBI_OK;
-    if (!tokens || !table || !route || top <= 0 || experts <= 0 || vocab <= 0 || (tile_rows != EG_M && tile_rows != TG_M))
+    if (!table || !route || top <= 0 || experts <= 0 || vocab <= 0 || (tile_rows != EG_M && tile_rows != TG_M))
         return CHIBI_ERR_ARGUMENT;
     const long long pairs = num_tokens * top;
     if (pairs > (1LL << 24) || experts > 4096)
@@ -736,8 +743,9 @@ CHIBI_API int chibi_route_by_table(const int* tokens, const int* table, int voca
     return launch_status();
 }
 
-// One product of the routed rows.  gated != 0: w [experts, 2 N, K], out = act(gate) * up in a's type;
-// else w [experts, N, K], out 32-bit.  gather != 0: row r of the product reads a[pair_of_row[r] / top].
+// One product of the routed rows.  gated 1: w [experts, 2 N, K], out = act(gate) * up in a's type;
+// gated 2: w [experts, N, K], out = act(sum) in a's type (the plain kernel only); gated 0: w [experts, N, K],
+// out 32-bit.  gather != 0: row r of the product reads a[pair_of_row[r] / top].
 // tile_rows is what the route was made with: 64 runs the plain kernel (any types and sizes; with
 // interleaved != 0 a gated matrix holds blocks of 16 gate rows and their 16 up rows), 128 the
 // tensor-core kernel (bfloat16, K a multiple of 32, gated matrices interleaved, N a multiple of 16).
@@ -758,7 +766,9 @@ CHIBI_API int chibi_expert_rows_gemm(const void* a, int a_type, long long a_stri
     const int* pair_of_row = offsets + experts + 1;
     const int* tile_expert = pair_of_row + 2 * pairs;
     const int* tile_row0 = tile_expert + max_tiles;
-    const long long w_stride = (long long)(gated ? 2 : 1) * N * K;
+    const long long w_stride = (long long)(gated == 1 ? 2 : 1) * N * K;
+    if (gated == 2 && tile_rows != EG_M)
+        return CHIBI_ERR_UNSUPPORTED;
     if (tile_rows == TG_M) {
         if (a_type != CHIBI_BF16 || w_type != CHIBI_BF16 || K % TG_K != 0 || a_stride % 8 != 0
             || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
@@ -784,20 +794,25 @@ CHIBI_API int chibi_expert_rows_gemm(const void* a, int a_type, long long a_stri
     }
     const dim3 grid((unsigned)((N + EG_N - 1) / EG_N), (unsigned)max_tiles);
     CHIBI_DISPATCH_TYPE(a_type, TA, CHIBI_DISPATCH_TYPE(w_type, TW, {
-        if (gated)
+        if (gated == 1)
             launch(expert_rows_gemm_kernel<TA, TW, TA, true>, grid, dim3(256), 0, stream, (const TA*)a, a_stride,
                    gather ? pair_of_row : (const int*)nullptr, top, (const TW*)w, w_stride, (TA*)out, out_stride,
                    offsets, tile_expert, tile_row0, N, K, kind, interleaved);
+        else if (gated == 2)
+            launch(expert_rows_gemm_kernel<TA, TW, TA, false>, grid, dim3(256), 0, stream, (const TA*)a, a_stride,
+                   gather ? pair_of_row : (const int*)nullptr, top, (const TW*)w, w_stride, (TA*)out, out_stride,
+                   offsets, tile_expert, tile_row0, N, K, kind, 0);
         else
             launch(expert_rows_gemm_kernel<TA, TW, float, false>, grid, dim3(256), 0, stream, (const TA*)a, a_stride,
                    gather ? pair_of_row : (const int*)nullptr, top, (const TW*)w, w_stride, (float*)out, out_stride,
-                   offsets, tile_expert, tile_row0, N, K, kind, 0);
+                   offsets, tile_expert, tile_row0, N, K, -1, 0);
     }));
     return launch_status();
 }
 
 CHIBI_API int chibi_combine_experts(const float* y, const int* route, float* acc, long long acc_stride,
-                                    long long tokens, int n, int top, int experts, float weight, cudaStream_t stream)
+                                    long long tokens, int n, int top, int experts, float weight,
+                                    const float* pair_weight, cudaStream_t stream)
 {
     if (tokens <= 0)
         return CHIBI_OK;
@@ -805,7 +820,7 @@ CHIBI_API int chibi_combine_experts(const float* y, const int* route, float* acc
         return CHIBI_ERR_ARGUMENT;
     const int* row_of_pair = route + experts + 1 + tokens * top;
     launch(combine_experts_kernel, dim3(blocks_for(tokens * n, 256)), dim3(256), 0, stream, y, row_of_pair, acc,
-           acc_stride, tokens, n, top, weight);
+           acc_stride, tokens, n, top, weight, pair_weight);
     return launch_status();
 }
 

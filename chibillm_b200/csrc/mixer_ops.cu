@@ -1,0 +1,607 @@
+// Kernels of the parts that a layer with norms on its sublayers' outputs, a token shift,
+// attention over cached latents, plain attention with biases / a norm over the whole
+// projection / an output gate, a gated linear recurrence and experts chosen by a router are
+// made of:
+//
+// * norm_rows: layer norm (mean taken off, variance = mean of the squared deviations, weight and
+//   bias) or RMS norm of 32-bit rows; the result replaces, or is added to, a 32-bit residual, and
+//   may be written in another type as well.
+// * token_shift: h[t] = x[t] + (x[t - 1] - x[t]) * w; the token before a step's first comes from
+//   the request's state, which then takes the step's last x.
+// * latent_prepare: from a row c_q | c | k_rot: RMS norm of c_q -> array; RMS norm of c and the
+//   rotation of k_rot -> one cache row k_rot | c.
+// * qkv_bias_norm_append: from a row q | k | v | ...: biases, RMS norm over the WHOLE q and the
+//   whole k (all heads at once, weights of that size), split-half rotation of every head's first
+//   features if asked; q -> array, k and v -> cache pages.
+// * sigmoid_gate: x *= sigmoid(g).
+// * recurrence_gates / gated_recurrence: q' = silu(q), f = l + (1 - l) sigmoid(f + b), v, all
+//   32-bit; then per head S <- diag(f) S + (1 - f) v^T, o = S^T q' over each sequence's tokens,
+//   from and to the request's state.
+// * router_top: the `top` largest of a row of router logits (ties to the lower index) and the
+//   softmax over them.
+//
+// Sums, norms, angles, gates and states are 32-bit whatever the activations' type is.
+#define CHIBI_UNIT mixer_ops
+#define CHIBI_UNIT_ID 11
+#include "common.cuh"
+
+namespace chibi {
+
+// ---------------------------------------------------------------- norm of rows
+// One block per row.  A thread touches the same columns in every pass.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+norm_rows_kernel(const float* __restrict__ y, const TW* __restrict__ w, const TW* __restrict__ b, float eps,
+                 float offset, int centered, float* residual, TO* __restrict__ out, int n)
+{
+    pdl_enter();
+    extern __shared__ float row[];
+    __shared__ float red[33];
+    const long long t = blockIdx.x;
+    const float* yr = y + t * n;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float v = yr[c];
+        row[c] = v;
+        s += v;
+    }
+    float mean = 0.f;
+    if (centered)
+        mean = block_sum(s, red) / (float)n;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float dv = row[c] - mean;
+        ss = fmaf(dv, dv, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        float v = (row[c] - mean) * inv * (to_f32(w[c]) + offset);
+        if (b)
+            v += to_f32(b[c]);
+        if (residual) {
+            v += residual[t * n + c];
+            residual[t * n + c] = v;
+        }
+        if (out)
+            out[t * n + c] = from_f32<TO>(v);
+    }
+}
+
+// ---------------------------------------------------------------- token shift
+// One block per token.  Only the block of a sequence's first token of the step touches the state:
+// every thread reads its columns of it and then replaces them by the step's last token's.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mix, float* __restrict__ state,
+                   const int* __restrict__ q_start, const int* __restrict__ seq_of_token,
+                   const int* __restrict__ state_slots, TO* __restrict__ out, int n)
+{
+    pdl_enter();
+    const long long t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    const int first = q_start[seq];
+    const float* xr = x + t * n;
+    TO* o = out + t * n;
+    if (t > first) {
+        const float* before = xr - n;
+        for (int c = threadIdx.x; c < n; c += blockDim.x) {
+            const float v = xr[c];
+            o[c] = from_f32<TO>(fmaf(before[c] - v, mix[c], v));
+        }
+        return;
+    }
+    const long long last = q_start[seq + 1] - 1;
+    float* st = state + (long long)state_slots[seq] * n;
+    const float* xl = x + last * n;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float v = xr[c];
+        const float before = st[c];
+        o[c] = from_f32<TO>(fmaf(before - v, mix[c], v));
+        st[c] = xl[c];
+    }
+}
+
+// ---------------------------------------------------------------- latents
+// One block per token.  Row: q_rank | kv_rank | rot columns (the last two only with a cache).
+template <typename TX, typename TC>
+__global__ void __launch_bounds__(128)
+latent_prepare_kernel(const TX* __restrict__ proj, long long stride, TX* __restrict__ cq, TC* __restrict__ k_cache,
+                      const float* __restrict__ q_norm, const float* __restrict__ kv_norm, float eps,
+                      const float* __restrict__ inv_freq, int q_rank, int kv_rank, int rot,
+                      const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                      const int* __restrict__ seq_rows, const int* __restrict__ block_table, int table_stride,
+                      int page_size, int num_pages, int* __restrict__ error)
+{
+    pdl_enter();
+    __shared__ float red[33];
+    const long long t = blockIdx.x;
+    const TX* row = proj + t * stride;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) {
+        const float v = to_f32(row[c]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
+        cq[t * q_rank + c] = from_f32<TX>(to_f32(row[c]) * inv * q_norm[c]);
+    if (!k_cache)
+        return;
+    const int pos = positions[t];
+    const int seq = seq_of_token[t];
+    const int table_row = seq_rows ? seq_rows[seq] : seq;
+    const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && error)
+            atomicExch(error, 2);
+        return;
+    }
+    TC* dst = k_cache + ((long long)page * page_size + pos % page_size) * (rot + kv_rank);
+    const TX* latent = row + q_rank;
+    ss = 0.f;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+        const float v = to_f32(latent[c]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x)
+        dst[rot + c] = from_f32<TC>(to_f32(latent[c]) * inv * kv_norm[c]);
+    const TX* shared = latent + kv_rank;
+    const int half = rot >> 1;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        const float u = to_f32(shared[j]), v = to_f32(shared[j + half]);
+        dst[j] = from_f32<TC>(u * cs - v * sn);
+        dst[j + half] = from_f32<TC>(v * cs + u * sn);
+    }
+}
+
+// ---------------------------------------------------------------- q | k | v: biases, whole norm, append
+// One block per token; shared memory holds q | k with their biases in 32-bit.
+template <typename TX, typename TC>
+__global__ void __launch_bounds__(256)
+qkv_bias_norm_append_kernel(const TX* __restrict__ proj, long long stride, TX* __restrict__ q_out,
+                            TC* __restrict__ k_cache, TC* __restrict__ v_cache, const float* __restrict__ bias,
+                            const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                            const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ seq_rows,
+                            const int* __restrict__ block_table, int table_stride, int nq, int nkv, int d, int dv,
+                            int page_size, int num_pages, int append, int* __restrict__ error)
+{
+    pdl_enter();
+    extern __shared__ float buf[];
+    __shared__ float red[33];
+    const long long t = blockIdx.x;
+    const TX* row = proj + t * stride;
+    const int qw = nq * d, kw = append ? nkv * d : 0, vw = append ? nkv * dv : 0;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < qw + kw; c += blockDim.x) {
+        const float v = to_f32(row[c]) + (bias ? bias[c] : 0.f);
+        buf[c] = v;
+        if (c < qw)
+            sq = fmaf(v, v, sq);
+        else
+            sk = fmaf(v, v, sk);
+    }
+    if (q_norm) {
+        sq = block_sum(sq, red);
+        const float inv = 1.f / sqrtf(sq / (float)qw + eps);
+        for (int c = threadIdx.x; c < qw; c += blockDim.x)
+            buf[c] *= inv * q_norm[c];
+    }
+    if (k_norm && append) {
+        sk = block_sum(sk, red);
+        const float inv = 1.f / sqrtf(sk / (float)kw + eps);
+        for (int c = qw + threadIdx.x; c < qw + kw; c += blockDim.x)
+            buf[c] *= inv * k_norm[c - qw];
+    }
+    __syncthreads();
+    const int pos = positions[t];
+    if (rot > 0) {
+        // k follows q in the buffer and both have heads of d features: head h starts at h * d
+        const int half = rot >> 1;
+        const int heads = nq + (append ? nkv : 0);
+        for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+            const int h = i / half, j = i - h * half;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[j], &sn, &cs);
+            float* p = buf + (size_t)h * d;
+            const float u = p[j], v = p[j + half];
+            p[j] = u * cs - v * sn;
+            p[j + half] = v * cs + u * sn;
+        }
+        __syncthreads();
+    }
+    for (int c = threadIdx.x; c < qw; c += blockDim.x)
+        q_out[t * qw + c] = from_f32<TX>(buf[c]);
+    if (!append)
+        return;
+    const int seq = seq_of_token[t];
+    const int table_row = seq_rows ? seq_rows[seq] : seq;
+    const int page = block_table[(size_t)table_row * table_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && error)
+            atomicExch(error, 2);
+        return;
+    }
+    const int slot = pos % page_size;
+    for (int c = threadIdx.x; c < kw; c += blockDim.x) {
+        const int h = c / d, j = c - h * d;
+        k_cache[(((long long)page * nkv + h) * page_size + slot) * d + j] = from_f32<TC>(buf[qw + c]);
+    }
+    for (int c = threadIdx.x; c < vw; c += blockDim.x) {
+        const int h = c / dv, j = c - h * dv;
+        const float v = to_f32(row[qw + kw + c]) + (bias ? bias[qw + kw + c] : 0.f);
+        v_cache[(((long long)page * nkv + h) * page_size + slot) * dv + j] = from_f32<TC>(v);
+    }
+}
+
+template <typename TX>
+__global__ void sigmoid_gate_kernel(TX* __restrict__ x, const TX* __restrict__ gate, long long gate_stride,
+                                    long long rows, int n)
+{
+    pdl_enter();
+    const long long total = rows * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / n;
+        const int c = (int)(i - t * n);
+        const float g = to_f32(gate[t * gate_stride + c]);
+        x[i] = from_f32<TX>(to_f32(x[i]) / (1.f + expf(-g)));
+    }
+}
+
+// ---------------------------------------------------------------- gated linear recurrence
+// out [T, 2 kw + vw] 32-bit: silu(q) | l + (1 - l) sigmoid(f + b) | v, from a row q | f | v.
+template <typename TX>
+__global__ void recurrence_gates_kernel(const TX* __restrict__ proj, long long stride, const float* __restrict__ bias,
+                                        const float* __restrict__ floor_, float* __restrict__ out, long long rows,
+                                        int kw, int vw)
+{
+    pdl_enter();
+    const int w = 2 * kw + vw;
+    const long long total = rows * w;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / w;
+        const int c = (int)(i - t * w);
+        const float v = to_f32(proj[t * stride + c]);
+        float r;
+        if (c < kw) {
+            r = v / (1.f + expf(-v));
+        } else if (c < 2 * kw) {
+            const float l = floor_[c - kw];
+            r = l + (1.f - l) / (1.f + expf(-(v + bias[c - kw])));
+        } else {
+            r = v;
+        }
+        out[i] = r;
+    }
+}
+
+// grid (blocks of GR_COLS value columns, heads, sequences); 128 threads: eight neighbouring lanes share
+// a value column, each with R of the head's key rows of it in registers (row = i * 8 + part) from the
+// sequence's first token of the step to its last.  The tokens' q', f and v come through two buffers of
+// shared memory in chunks of GR_CHUNK tokens, the next chunk on its way (cp.async) while this one runs.
+constexpr int GR_COLS = 16, GR_PARTS = 8, GR_CHUNK = 16, GR_THREADS = GR_COLS * GR_PARTS;
+
+__device__ __forceinline__ void gr_copy4(float* dst, const float* src)
+{
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(src) : "memory");
+}
+
+template <int R>
+__global__ void __launch_bounds__(GR_THREADS)
+gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state, float* __restrict__ out,
+                        const int* __restrict__ q_start, const int* __restrict__ state_slots, int heads, int d, int e)
+{
+    pdl_enter();
+    extern __shared__ float sm[];
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int t0 = q_start[seq], t1 = q_start[seq + 1];
+    if (t1 <= t0)
+        return;
+    const int tid = threadIdx.x;
+    const int col_in = tid / GR_PARTS, part = tid % GR_PARTS;
+    const int col = blockIdx.x * GR_COLS + col_in;
+    const int kw = heads * d, vw = heads * e;
+    const int width = 2 * kw + vw;
+    const int per_token = 2 * d + GR_COLS;                 // q' | f of the head, v of the block's columns
+    float* bufs[2] = {sm, sm + GR_CHUNK * per_token};
+    float S[R];
+    float* st = state + (((long long)state_slots[seq] * heads + head) * d) * e;
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int r = i * GR_PARTS + part;
+        S[i] = (r < d && col < e) ? st[(long long)r * e + col] : 0.f;
+    }
+    auto fetch = [&](int first, float* buf) {
+        const int count = min(GR_CHUNK, t1 - first);
+        for (int i = tid; i < count * per_token; i += GR_THREADS) {
+            const int tok = i / per_token, w = i - tok * per_token;
+            const float* src = qfv + (long long)(first + tok) * width;
+            if (w < d)
+                src += head * d + w;
+            else if (w < 2 * d)
+                src += kw + head * d + (w - d);
+            else {
+                const int c = blockIdx.x * GR_COLS + (w - 2 * d);
+                src += 2 * kw + head * e + (c < e ? c : e - 1);
+            }
+            gr_copy4(buf + i, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(t0, bufs[0]);
+    int which = 0;
+    for (int first = t0; first < t1; first += GR_CHUNK, which ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();            // this chunk has arrived, and everyone has left the other buffer
+        if (first + GR_CHUNK < t1)
+            fetch(first + GR_CHUNK, bufs[which ^ 1]);
+        const float* buf = bufs[which];
+        const int count = min(GR_CHUNK, t1 - first);
+        for (int tok = 0; tok < count; ++tok) {
+            const float* q = buf + tok * per_token + part;
+            const float* f = q + d;
+            const float v = buf[tok * per_token + 2 * d + col_in];
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                if (i * GR_PARTS + part < d) {
+                    const float fi = f[i * GR_PARTS];
+                    S[i] = fmaf(fi, S[i], (1.f - fi) * v);
+                    acc = fmaf(S[i], q[i * GR_PARTS], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (part == 0 && col < e)
+                out[(long long)(first + tok) * vw + head * e + col] = acc;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int r = i * GR_PARTS + part;
+        if (r < d && col < e)
+            st[(long long)r * e + col] = S[i];
+    }
+}
+
+// ---------------------------------------------------------------- router
+// One warp per token; shared memory: the warp's copy of its row.
+constexpr int ROUTER_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_top_kernel(const float* __restrict__ logits, long long stride, int* __restrict__ chosen,
+                  float* __restrict__ share, long long tokens, int experts, int top)
+{
+    pdl_enter();
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * ROUTER_WARPS + warp;
+    if (t >= tokens)
+        return;
+    float* vals = sm + (size_t)warp * (experts + top);
+    float* picked = vals + experts;
+    for (int e = lane; e < experts; e += 32)
+        vals[e] = logits[t * stride + e];
+    __syncwarp();
+    for (int s = 0; s < top; ++s) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = vals[e];
+            if (v > best) {                                // a lane meets its experts in rising order
+                best = v;
+                at = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ov > best || (ov == best && oa < at)) {
+                best = ov;
+                at = oa;
+            }
+        }
+        if (at == 0x7fffffff)
+            at = s;                                        // a row without a finite number left
+        if (lane == 0) {
+            chosen[t * top + s] = at;
+            picked[s] = best;
+            vals[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float m = picked[0];
+        float sum = 0.f;
+        for (int s = 0; s < top; ++s)
+            sum += expf(picked[s] - m);
+        for (int s = 0; s < top; ++s)
+            share[t * top + s] = expf(picked[s] - m) / sum;
+    }
+}
+
+static inline unsigned grid_for(long long total, int threads)
+{
+    long long b = (total + threads - 1) / threads;
+    if (b < 1)
+        b = 1;
+    return (unsigned)(b > 148LL * 16 ? 148LL * 16 : b);
+}
+
+} // namespace chibi
+
+using namespace chibi;
+
+CHIBI_API int chibi_norm_rows(const float* y, const void* w, const void* b, int w_type, float eps, float offset,
+                              int centered, float* residual, void* out, int out_type, long long rows, int n,
+                              cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    if (!y || !w || n <= 0 || (!residual && !out))
+        return CHIBI_ERR_ARGUMENT;
+    const size_t smem = (size_t)n * sizeof(float);
+    if (smem > 200 * 1024 || rows > 2147483647LL)
+        return CHIBI_ERR_UNSUPPORTED;
+    CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(out_type, TO, {
+        auto kernel = norm_rows_kernel<TW, TO>;
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch(kernel, dim3((unsigned)rows), dim3(256), smem, stream, y, (const TW*)w, (const TW*)b, eps, offset,
+               centered, residual, (TO*)out, n);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_token_shift(const float* x, const float* mix, float* state, const int* q_start,
+                                const int* seq_of_token, const int* state_slots, void* out, int out_type,
+                                long long rows, int n, cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    if (!x || !mix || !state || !q_start || !seq_of_token || !state_slots || !out || n <= 0 || rows > 2147483647LL)
+        return CHIBI_ERR_ARGUMENT;
+    CHIBI_DISPATCH_TYPE(out_type, TO, {
+        launch(token_shift_kernel<TO>, dim3((unsigned)rows), dim3(256), 0, stream, x, mix, state, q_start, seq_of_token,
+               state_slots, (TO*)out, n);
+    });
+    return launch_status();
+}
+
+CHIBI_API int chibi_latent_prepare(const void* proj, int x_type, long long stride, void* cq, void* k_cache,
+                                   int cache_type, const float* q_norm, const float* kv_norm, float eps,
+                                   const float* inv_freq, int q_rank, int kv_rank, int rot, const int* positions,
+                                   const int* seq_of_token, const int* seq_rows, const int* block_table,
+                                   int table_stride, int page_size, int num_pages, long long rows, int* error,
+                                   cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    if (!proj || !cq || !q_norm || q_rank <= 0 || rows > 2147483647LL)
+        return CHIBI_ERR_ARGUMENT;
+    if (k_cache && (!kv_norm || !inv_freq || !positions || !seq_of_token || !block_table || kv_rank <= 0 || rot <= 0
+                    || rot % 2 || page_size <= 0))
+        return CHIBI_ERR_ARGUMENT;
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(cache_type, TC, {
+        launch(latent_prepare_kernel<TX, TC>, dim3((unsigned)rows), dim3(128), 0, stream, (const TX*)proj, stride,
+               (TX*)cq, (TC*)k_cache, q_norm, kv_norm, eps, inv_freq, q_rank, kv_rank, rot, positions, seq_of_token,
+               seq_rows, block_table, table_stride, page_size, num_pages, error);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_qkv_bias_norm_append(const void* proj, int x_type, long long stride, void* q_out, void* k_cache,
+                                         void* v_cache, int cache_type, const float* bias, const float* q_norm,
+                                         const float* k_norm, float eps, const float* inv_freq, int rot,
+                                         const int* positions, const int* seq_of_token, const int* seq_rows,
+                                         const int* block_table, int table_stride, int nq, int nkv, int d, int dv,
+                                         int page_size, int num_pages, long long rows, int* error, cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    const int append = k_cache != nullptr;
+    if (!proj || !q_out || !positions || nq <= 0 || nkv <= 0 || d <= 0 || dv <= 0 || rot < 0 || rot % 2 || rot > d
+        || (rot > 0 && !inv_freq) || rows > 2147483647LL)
+        return CHIBI_ERR_ARGUMENT;
+    if (append && (!v_cache || !seq_of_token || !block_table || page_size <= 0))
+        return CHIBI_ERR_ARGUMENT;
+    const size_t smem = (size_t)(nq + (append ? nkv : 0)) * d * sizeof(float);
+    if (smem > 200 * 1024)
+        return CHIBI_ERR_UNSUPPORTED;
+    CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(cache_type, TC, {
+        auto kernel = qkv_bias_norm_append_kernel<TX, TC>;
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch(kernel, dim3((unsigned)rows), dim3(256), smem, stream, (const TX*)proj, stride, (TX*)q_out,
+               (TC*)k_cache, (TC*)v_cache, bias, q_norm, k_norm, eps, inv_freq, rot, positions, seq_of_token, seq_rows,
+               block_table, table_stride, nq, nkv, d, dv, page_size, num_pages, append, error);
+    }));
+    return launch_status();
+}
+
+CHIBI_API int chibi_sigmoid_gate(void* x, const void* gate, int x_type, long long gate_stride, long long rows, int n,
+                                 cudaStream_t stream)
+{
+    if (rows <= 0 || n <= 0)
+        return CHIBI_OK;
+    if (!x || !gate)
+        return CHIBI_ERR_ARGUMENT;
+    CHIBI_DISPATCH_TYPE(x_type, TX, {
+        launch(sigmoid_gate_kernel<TX>, dim3(grid_for(rows * n, 256)), dim3(256), 0, stream, (TX*)x, (const TX*)gate,
+               gate_stride, rows, n);
+    });
+    return launch_status();
+}
+
+CHIBI_API int chibi_recurrence_gates(const void* proj, int x_type, long long stride, const float* bias,
+                                     const float* floor_, float* out, long long rows, int kw, int vw,
+                                     cudaStream_t stream)
+{
+    if (rows <= 0)
+        return CHIBI_OK;
+    if (!proj || !bias || !floor_ || !out || kw <= 0 || vw <= 0)
+        return CHIBI_ERR_ARGUMENT;
+    CHIBI_DISPATCH_TYPE(x_type, TX, {
+        launch(recurrence_gates_kernel<TX>, dim3(grid_for(rows * (2LL * kw + vw), 256)), dim3(256), 0, stream,
+               (const TX*)proj, stride, bias, floor_, out, rows, kw, vw);
+    });
+    return launch_status();
+}
+
+CHIBI_API int chibi_gated_recurrence(const float* qfv, float* state, float* out, const int* q_start,
+                                     const int* state_slots, int seqs, int heads, int d, int e, cudaStream_t stream)
+{
+    if (seqs <= 0)
+        return CHIBI_OK;
+    if (!qfv || !state || !out || !q_start || !state_slots || heads <= 0 || d <= 0 || e <= 0)
+        return CHIBI_ERR_ARGUMENT;
+    if (d > 32 * GR_PARTS || heads > 65535 || seqs > 65535)
+        return CHIBI_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)((e + GR_COLS - 1) / GR_COLS), (unsigned)heads, (unsigned)seqs);
+    const size_t smem = (size_t)2 * GR_CHUNK * (2 * d + GR_COLS) * sizeof(float);
+#define CHIBI_GR_LAUNCH(R)                                                                                       \
+    do {                                                                                                         \
+        auto kernel = gated_recurrence_kernel<R>;                                                                \
+        if (smem > 48 * 1024)                                                                                    \
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
+        launch(kernel, grid, dim3(GR_THREADS), smem, stream, qfv, state, out, q_start, state_slots, heads, d, e); \
+    } while (0)
+    if (d <= 4 * GR_PARTS)
+        CHIBI_GR_LAUNCH(4);
+    else if (d <= 8 * GR_PARTS)
+        CHIBI_GR_LAUNCH(8);
+    else if (d <= 16 * GR_PARTS)
+        CHIBI_GR_LAUNCH(16);
+    else
+        CHIBI_GR_LAUNCH(32);
+#undef CHIBI_GR_LAUNCH
+    return launch_status();
+}
+
+CHIBI_API int chibi_router_top(const float* logits, long long stride, int* chosen, float* share, long long tokens,
+                               int experts, int top, cudaStream_t stream)
+{
+    if (tokens <= 0)
+        return CHIBI_OK;
+    if (!logits || !chosen || !share || experts <= 0 || top <= 0 || top > experts)
+        return CHIBI_ERR_ARGUMENT;
+    const size_t smem = (size_t)ROUTER_WARPS * (experts + top) * sizeof(float);
+    if (smem > 48 * 1024)
+        return CHIBI_ERR_UNSUPPORTED;
+    const long long blocks = (tokens + ROUTER_WARPS - 1) / ROUTER_WARPS;
+    if (blocks > 2147483647LL)
+        return CHIBI_ERR_UNSUPPORTED;
+    launch(router_top_kernel, dim3((unsigned)blocks), dim3(ROUTER_WARPS * 32), smem, stream, logits, stride, chosen,
+           share, tokens, experts, top);
+    return launch_status();
+}

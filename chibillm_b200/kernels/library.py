@@ -45,7 +45,7 @@ _SIGNATURES = {
         "chibi_reduce_swiglu": [P, I, I, I, P, I, I, P],
         "chibi_qk_norm_rope_append_partial": [P, I, L, L, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I,
                                               I, I, F, F, I, P, P],
-        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, I, F, I, I, F, P, P, P, P],
+        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, I, F, I, I, F, P, P, P, P, P],
         "chibi_short_conv": [P, I, L, P, P, P, P, L, P, P, I, I, I, I, P],
         "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
         "chibi_decay_logits": [P, I, L, P, P, L, I, I, P],
@@ -60,7 +60,15 @@ _SIGNATURES = {
         "chibi_gated_activation": [P, I, L, P, I, P, L, I, I, I, P],
         "chibi_route_by_table": [P, P, I, I, I, L, I, P, P, P],
         "chibi_expert_rows_gemm": [P, I, L, I, I, P, I, P, L, P, L, I, I, I, I, I, I, I, P],
-        "chibi_combine_experts": [P, P, P, L, L, I, I, I, F, P],
+        "chibi_combine_experts": [P, P, P, L, L, I, I, I, F, P, P],
+        "chibi_norm_rows": [P, P, P, I, F, F, I, P, P, I, L, I, P],
+        "chibi_token_shift": [P, P, P, P, P, P, P, I, L, I, P],
+        "chibi_latent_prepare": [P, I, L, P, P, I, P, P, F, P, I, I, I, P, P, P, P, I, I, I, L, P, P],
+        "chibi_qkv_bias_norm_append": [P, I, L, P, P, P, I, P, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, L, P, P],
+        "chibi_sigmoid_gate": [P, P, I, L, L, I, P],
+        "chibi_recurrence_gates": [P, I, L, P, P, P, L, I, I, P],
+        "chibi_gated_recurrence": [P, P, P, P, P, I, I, I, I, P],
+        "chibi_router_top": [P, L, P, P, L, I, I, P],
         "chibi_layer_end": [P, P, F, P, P, L, I, I, P, P, P, P, I, I, F, P, F, P, P, I, I, L, I, P, P],
         "chibi_side_gate": [P, I, L, P, P, I, L, I, I, L, I, I, P, P],
         "chibi_softcap": [P, F, L, P],

@@ -755,7 +755,8 @@ class CudaKernels:
                   nq: int, nkv: int, d: int, page_size: int, scale: float,
                   window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0,
                   seq_rows: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
-                  distance_bias=None, chunk: Optional[int] = None, value_dim: Optional[int] = None) -> None:
+                  distance_bias=None, chunk: Optional[int] = None, value_dim: Optional[int] = None,
+                  sink: Optional[torch.Tensor] = None) -> None:
         """Causal attention of every token over its sequence's pages.  bfloat16
         with a head size that is a multiple of 16 runs on the tensor cores (one
         library per head size, compiled when first needed); everything else, the
@@ -766,9 +767,12 @@ class CudaKernels:
         query sees only the keys of its own block of C positions, counted from the
         sequence's start.  ``value_dim``: the size of a value head where it is not d
         (the value cache is [pages, nkv, page, value_dim], out [T, nq * value_dim]);
-        such a layer runs the plain kernel."""
+        such a layer runs the plain kernel.  ``sink``, float32 [nq]: exp(sink[h]) joins the
+        softmax's denominator of head h (unscaled, once, with no value)."""
         _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions,
-                   seq_rows)
+                   seq_rows, sink)
+        if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_contiguous()):
+            raise KernelError("attention: the sink is a contiguous float32 [nq] tensor")
         r1 = r2 = None
         if distance_bias is not None:
             r1, r2 = distance_bias
@@ -794,7 +798,7 @@ class CudaKernels:
             raise KernelError(f"attention: cache shapes {tuple(k_cache.shape)} / {tuple(v_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
         if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-                and d % 16 == 0 and d <= 256 and dv == d):
+                and d % 16 == 0 and d <= 256 and dv == d and sink is None):
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                                 page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows, cap, r1, r2,
                                 chunk)
@@ -805,8 +809,8 @@ class CudaKernels:
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
             _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, dv, page_size,
             k_cache.shape[0],
-            float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(self.error), self._stream()),
-            "attention")
+            float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(sink), _ptr(self.error),
+            self._stream()), "attention")
 
     def decode_attention_splits(self, seqs: int, nq: int, nkv: int, max_ctx_len: int) -> int:
         """Key ranges per sequence of the decode attention kernel: as many CTAs as
@@ -1089,7 +1093,7 @@ class CudaKernels:
         _check(self.lib.chibi_add_row_vector(_ptr(acc), acc.stride(0), _ptr(vec), acc.shape[0], acc.shape[1],
                                              self._stream()), "add_row_vector")
 
-    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "tanh": 4}
+    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "tanh": 4, "relu2": 5}
 
     _EPILOGUE_ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}    # what a product's epilogue takes
 
@@ -1276,7 +1280,7 @@ class CudaKernels:
                 _check(self.lib.chibi_expert_rows_tc(_ptr(act), _ptr(down), _ptr(y), D, _ptr(route), pairs, E, D, F, 0,
                                                      0, _ptr(self.error), stream), "routed_experts (down, tcgen05)")
                 _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
-                                                      float(weight), stream), "routed_experts (combine)")
+                                                      float(weight), None, stream), "routed_experts (combine)")
                 self.tensor_core_calls += 2
                 return
             if s1 != -2:
@@ -1290,7 +1294,7 @@ class CudaKernels:
         if fast:
             self.tensor_core_calls += 2
         _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
-                                              float(weight), stream), "routed_experts (combine)")
+                                              float(weight), None, stream), "routed_experts (combine)")
 
     def combine_experts(self, y: torch.Tensor, route: torch.Tensor, acc: torch.Tensor, top: int, experts: int,
                         weight: float) -> None:
@@ -1305,7 +1309,218 @@ class CudaKernels:
         _rows_contiguous(acc, "combine_experts: acc")
         self.launches += 1
         _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, experts,
-                                              float(weight), self._stream()), "combine_experts")
+                                              float(weight), None, self._stream()), "combine_experts")
+
+    # ---- parts of mixer_ops.cu
+    def norm_rows(self, y: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, offset: float,
+                  centered: bool, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> None:
+        """v = norm(y) * (weight + offset) + bias over the rows of the float32 y [T, n]:
+        ``centered`` takes the mean off first and divides by the root of the mean squared
+        deviation + eps (layer norm), else by the root of the mean square + eps.  With
+        ``residual`` (float32 [T, n]) residual += v and ``out``, if given, takes the new
+        residual in its own type; without it ``out`` takes v."""
+        _need_cuda(y, weight, bias, residual, out)
+        if y.dim() != 2 or y.dtype != torch.float32 or not y.is_contiguous():
+            raise KernelError("norm_rows: y is contiguous float32 [T, n]")
+        T, n = y.shape
+        if weight.shape != (n,) or not weight.is_contiguous() or (bias is not None and (
+                bias.shape != (n,) or bias.dtype != weight.dtype or not bias.is_contiguous())):
+            raise KernelError("norm_rows: weight and bias are contiguous [n] of one type")
+        for t, what in ((residual, "residual"), (out, "out")):
+            if t is not None and (t.shape != (T, n) or not t.is_contiguous()):
+                raise KernelError(f"norm_rows: {what} is contiguous [T, n]")
+        if residual is None and out is None:
+            raise KernelError("norm_rows: nowhere to write")
+        if residual is not None and residual.dtype != torch.float32:
+            raise KernelError("norm_rows: the residual is float32")
+        self.launches += 1
+        _check(self.lib.chibi_norm_rows(_ptr(y), _ptr(weight), _ptr(bias), _code(weight), float(eps), float(offset),
+                                        1 if centered else 0, _ptr(residual), _ptr(out),
+                                        _code(out) if out is not None else F32, T, n, self._stream()), "norm_rows")
+
+    def token_shift(self, x: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+                    seq_of_token: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t] = x[t] + (x[t - 1] - x[t]) * mix for the float32 x [T, n]; the token before a
+        sequence's first of this step is ``state[slot]`` (float32 [slots, n]), which then
+        takes the sequence's last x of this step."""
+        _need_cuda(x, mix, state, q_start, seq_of_token, state_slots, out)
+        T, n = x.shape
+        if (x.dtype != torch.float32 or not x.is_contiguous() or mix.dtype != torch.float32 or mix.shape != (n,)
+                or state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != n or not state.is_contiguous()
+                or out.shape != (T, n) or not out.is_contiguous()):
+            raise KernelError("token_shift: shapes or types")
+        self.launches += 1
+        _check(self.lib.chibi_token_shift(_ptr(x), _ptr(mix), _ptr(state), _ptr(q_start), _ptr(seq_of_token),
+                                          _ptr(state_slots), _ptr(out), _code(out), T, n, self._stream()),
+               "token_shift")
+
+    def latent_prepare(self, proj: torch.Tensor, cq: torch.Tensor, k_cache: Optional[torch.Tensor],
+                       q_norm: torch.Tensor, kv_norm: Optional[torch.Tensor], eps: float,
+                       inv_freq: Optional[torch.Tensor], q_rank: int, kv_rank: int, rot: int, positions: torch.Tensor,
+                       seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,
+                       seq_rows: Optional[torch.Tensor] = None) -> None:
+        """From rows c_q | c | k_rot ([T, q_rank + kv_rank + rot]; [T, q_rank] without a
+        cache): cq = RMSNorm(c_q) * q_norm; the cache row of the token's position
+        ([pages, 1, page, rot + kv_rank]) takes the rotated k_rot, then RMSNorm(c) * kv_norm."""
+        _need_cuda(proj, cq, k_cache, q_norm, kv_norm, inv_freq, positions, seq_of_token, block_table, seq_rows)
+        _rows_contiguous(proj, "latent_prepare: proj")
+        T = proj.shape[0]
+        append = k_cache is not None
+        if proj.shape[1] < q_rank + (kv_rank + rot if append else 0) or cq.shape != (T, q_rank) \
+                or not cq.is_contiguous() or cq.dtype != proj.dtype or q_norm.dtype != torch.float32 \
+                or q_norm.numel() != q_rank:
+            raise KernelError("latent_prepare: shapes or types")
+        num_pages = table_stride = 0
+        if append:
+            if (tuple(k_cache.shape[1:]) != (1, page_size, rot + kv_rank) or not k_cache.is_contiguous()
+                    or kv_norm is None or kv_norm.dtype != torch.float32 or kv_norm.numel() != kv_rank
+                    or inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot // 2):
+                raise KernelError("latent_prepare: cache, norm weight or frequencies")
+            num_pages = k_cache.shape[0]
+            _rows_contiguous(block_table, "latent_prepare: block_table")
+            table_stride = block_table.stride(0)
+        self.launches += 1
+        _check(self.lib.chibi_latent_prepare(
+            _ptr(proj), _code(proj), proj.stride(0), _ptr(cq), _ptr(k_cache), _code(k_cache) if append else F32,
+            _ptr(q_norm), _ptr(kv_norm), float(eps), _ptr(inv_freq), q_rank, kv_rank, rot, _ptr(positions),
+            _ptr(seq_of_token), _ptr(seq_rows), _ptr(block_table), table_stride, page_size, num_pages, T,
+            _ptr(self.error), self._stream()), "latent_prepare")
+
+    def qkv_bias_norm_append(self, proj: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                             v_cache: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                             q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: Optional[float],
+                             inv_freq: Optional[torch.Tensor], rot: int, positions: torch.Tensor,
+                             seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], nq: int, nkv: int, d: int,
+                             dv: int, page_size: int, seq_rows: Optional[torch.Tensor] = None) -> None:
+        """From rows q | k | v | ... ([T, >= nq d + nkv d + nkv dv]; q only without a
+        cache): + bias (float32, as wide as what is read), q and k each divided by the root
+        mean square of their WHOLE width and multiplied by q_norm / k_norm (float32; None:
+        no norm), the first ``rot`` features of every head rotated; q -> q_out, k and v ->
+        cache pages ([pages, nkv, page, d] and [.., dv])."""
+        _need_cuda(proj, q_out, k_cache, v_cache, bias, q_norm, k_norm, inv_freq, positions, seq_of_token,
+                   block_table, seq_rows)
+        _rows_contiguous(proj, "qkv_bias_norm_append: proj")
+        T = proj.shape[0]
+        append = k_cache is not None
+        width = nq * d + (nkv * (d + dv) if append else 0)
+        if proj.shape[1] < width or q_out.shape != (T, nq * d) or not q_out.is_contiguous() or q_out.dtype != proj.dtype:
+            raise KernelError("qkv_bias_norm_append: proj / q_out shapes or types")
+        for t, n in ((bias, width), (q_norm, nq * d), (k_norm, nkv * d)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() < n or not t.is_contiguous()):
+                raise KernelError("qkv_bias_norm_append: bias and norm weights are contiguous float32")
+        if rot and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rot // 2):
+            raise KernelError("qkv_bias_norm_append: inv_freq must hold rot/2 float32 values")
+        num_pages = table_stride = 0
+        if append:
+            if (v_cache is None or not k_cache.is_contiguous() or not v_cache.is_contiguous()
+                    or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
+                    or tuple(v_cache.shape) != (k_cache.shape[0], nkv, page_size, dv) or v_cache.dtype != k_cache.dtype
+                    or (q_norm is not None and k_norm is None)):
+                raise KernelError(f"qkv_bias_norm_append: cache shapes {tuple(k_cache.shape)}")
+            num_pages = k_cache.shape[0]
+            _rows_contiguous(block_table, "qkv_bias_norm_append: block_table")
+            table_stride = block_table.stride(0)
+        self.launches += 1
+        _check(self.lib.chibi_qkv_bias_norm_append(
+            _ptr(proj), _code(proj), proj.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+            _code(k_cache) if append else F32, _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps or 0.0),
+            _ptr(inv_freq), int(rot), _ptr(positions), _ptr(seq_of_token), _ptr(seq_rows), _ptr(block_table),
+            table_stride, nq, nkv, d, dv, page_size, num_pages, T, _ptr(self.error), self._stream()),
+            "qkv_bias_norm_append")
+
+    def sigmoid_gate(self, x: torch.Tensor, gate: torch.Tensor) -> None:
+        """x *= sigmoid(gate), in place; x contiguous [T, n], gate [T, n] with contiguous rows."""
+        _need_cuda(x, gate)
+        _rows_contiguous(gate, "sigmoid_gate: gate")
+        if not x.is_contiguous() or gate.shape != x.shape or gate.dtype != x.dtype:
+            raise KernelError("sigmoid_gate: shapes or types")
+        self.launches += 1
+        _check(self.lib.chibi_sigmoid_gate(_ptr(x), _ptr(gate), _code(x), gate.stride(0), x.shape[0], x.shape[1],
+                                           self._stream()), "sigmoid_gate")
+
+    def recurrence_gates(self, proj: torch.Tensor, bias: torch.Tensor, floor: torch.Tensor, out: torch.Tensor,
+                         kw: int) -> None:
+        """From rows q | f | v ([T, 2 kw + vw]): out (float32, same shape) = silu(q) |
+        floor + (1 - floor) * sigmoid(f + bias) | v."""
+        _need_cuda(proj, bias, floor, out)
+        _rows_contiguous(proj, "recurrence_gates: proj")
+        T, w = proj.shape
+        vw = w - 2 * kw
+        if vw <= 0 or out.shape != (T, w) or out.dtype != torch.float32 or not out.is_contiguous() \
+                or bias.dtype != torch.float32 or floor.dtype != torch.float32 or bias.numel() != kw \
+                or floor.numel() != kw:
+            raise KernelError("recurrence_gates: shapes or types")
+        self.launches += 1
+        _check(self.lib.chibi_recurrence_gates(_ptr(proj), _code(proj), proj.stride(0), _ptr(bias), _ptr(floor),
+                                               _ptr(out), T, kw, vw, self._stream()), "recurrence_gates")
+
+    def gated_recurrence(self, qfv: torch.Tensor, state: torch.Tensor, o: torch.Tensor, q_start: torch.Tensor,
+                         state_slots: torch.Tensor, heads: int, d: int, e: int, max_q_len: int = 0) -> None:
+        """Per sequence and head, over the step's tokens in order: S <- diag(f) S + (1 - f) v^T,
+        o = S^T q, with q | f | v the float32 rows of ``qfv`` [T, 2 heads d + heads e] as
+        ``recurrence_gates`` makes them and S = state[slot, head] (float32 [slots, heads, d, e]),
+        read at the start and written back at the end.  o: float32 [T, heads e]."""
+        _need_cuda(qfv, state, o, q_start, state_slots)
+        T = qfv.shape[0]
+        if (qfv.dtype != torch.float32 or not qfv.is_contiguous() or qfv.shape[1] != heads * (2 * d + e)
+                or state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, d, e) or not state.is_contiguous()
+                or o.shape != (T, heads * e) or o.dtype != torch.float32 or not o.is_contiguous()):
+            raise KernelError("gated_recurrence: shapes or types")
+        self.launches += 1
+        _check(self.lib.chibi_gated_recurrence(_ptr(qfv), _ptr(state), _ptr(o), _ptr(q_start), _ptr(state_slots),
+                                               q_start.numel() - 1, heads, d, e, self._stream()), "gated_recurrence")
+
+    def router_top(self, logits: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor) -> None:
+        """chosen[t] (int32 [T, top]) = the experts with the largest logits[t] (float32 [T, E]),
+        largest first, ties to the lower number; share[t] = softmax over those logits."""
+        _need_cuda(logits, chosen, share)
+        _rows_contiguous(logits, "router_top: logits")
+        T, E = logits.shape
+        top = chosen.shape[1]
+        if logits.dtype != torch.float32 or chosen.dtype != torch.int32 or share.dtype != torch.float32 \
+                or chosen.shape != (T, top) or share.shape != (T, top) or not chosen.is_contiguous() \
+                or not share.is_contiguous() or not (0 < top <= E):
+            raise KernelError("router_top: shapes or types")
+        self.launches += 1
+        _check(self.lib.chibi_router_top(_ptr(logits), logits.stride(0), _ptr(chosen), _ptr(share), T, E, top,
+                                         self._stream()), "router_top")
+
+    def chosen_experts(self, x: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, up: torch.Tensor,
+                       down: torch.Tensor, acc: torch.Tensor, route: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
+                       kind: str, sorted_x: Optional[torch.Tensor] = None) -> None:
+        """acc[t] += sum over s of share[t, s] * down_e (act(up_e x[t])), e = chosen[t, s]; up
+        [E, F, D], down [E, D, F]; scratch as for ``routed_experts``.  The (token, choice)
+        pairs are sorted by expert on the device and the two products run over tiles of one
+        expert's rows; nothing is read on the host."""
+        _need_cuda(x, chosen, share, up, down, acc, route, act, y)
+        _rows_contiguous(x, "chosen_experts: x")
+        _rows_contiguous(acc, "chosen_experts: acc")
+        T, D = x.shape
+        E, F, _ = up.shape
+        top = chosen.shape[1]
+        pairs = T * top
+        if (up.shape != (E, F, D) or down.shape != (E, D, F) or not up.is_contiguous() or not down.is_contiguous()
+                or down.dtype != up.dtype or chosen.dtype != torch.int32 or chosen.shape != (T, top)
+                or not chosen.is_contiguous() or share.shape != (T, top) or share.dtype != torch.float32
+                or not share.is_contiguous() or acc.dtype != torch.float32 or acc.shape != (T, D)
+                or route.dtype != torch.int32 or route.numel() < self.route_words(pairs, E)
+                or act.shape != (pairs, F) or act.dtype != x.dtype or not act.is_contiguous()
+                or y.shape != (pairs, D) or y.dtype != torch.float32 or not y.is_contiguous()
+                or kind not in self.ACTIVATIONS):
+            raise KernelError("chosen_experts: shapes or types")
+        stream = self._stream()
+        self.launches += 4
+        tile = self._expert_tile_rows[0]
+        _check(self.lib.chibi_route_by_table(None, _ptr(chosen), T, top, E, T, tile, _ptr(route), _ptr(self.error),
+                                             stream), "chosen_experts (route)")
+        _check(self.lib.chibi_expert_rows_gemm(_ptr(x), _code(x), x.stride(0), 1, top, _ptr(up), _code(up), _ptr(act),
+                                               F, _ptr(route), pairs, E, F, D, 2, self.ACTIVATIONS[kind], tile, 0,
+                                               stream), "chosen_experts (up)")
+        _check(self.lib.chibi_expert_rows_gemm(_ptr(act), _code(act), F, 0, top, _ptr(down), _code(down), _ptr(y), D,
+                                               _ptr(route), pairs, E, D, F, 0, 0, tile, 0, stream),
+               "chosen_experts (down)")
+        _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E, 1.0,
+                                              _ptr(share), stream), "chosen_experts (combine)")
 
     def layer_end(self, residual: torch.Tensor, delta: Optional[torch.Tensor], mult: float, side=None,
                   y_in: Optional[torch.Tensor] = None, norm=None, copy_out: Optional[torch.Tensor] = None) -> None:

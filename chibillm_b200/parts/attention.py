@@ -26,6 +26,14 @@ key and value projections that only ever reads another run step's cache
 amplitude.  The last two, and a value size of its own, take the plain order of
 kernels: the q | k | v product, one kernel that rotates, normalises and appends,
 attention, the output product.
+
+A sink (``sink``: one learned number per query head in the softmax's denominator)
+goes to the attention kernels as it is.  Biases on q, k and v, a norm of q and k
+over their whole projections (all heads at once) and a sigmoid gate on the
+concatenated heads (``biases``, ``whole_norm_eps``, ``output_gate``) take an order
+of their own: one product gives q | k | v | gate, one kernel adds the biases,
+normalises, rotates if there is a rotation, writes q and appends k and v, attention
+follows, one kernel multiplies by sigmoid(gate), then the output product.
 """
 from __future__ import annotations
 
@@ -61,9 +69,20 @@ class PagedAttention(Mixer):
         # the plain order of kernels (see the module's text)
         self.rotate_then_norm = (spec.unit_norm_eps is not None or self.value_dim != spec.head_dim
                                  or getattr(self.position, "amplitude", 1.0) != 1.0)
+        # biases, a norm over the whole projections or an output gate: the order of the module's last paragraph
+        self.bias_norm_gate = spec.biases or spec.whole_norm_eps is not None or spec.output_gate
+        if self.bias_norm_gate:
+            if spec.tied_values or spec.qk_norm is not None or spec.unit_norm_eps is not None \
+                    or getattr(self.position, "amplitude", 1.0) != 1.0:
+                raise ValueError("biases, a norm over the whole projection and an output gate are not combined with "
+                                 "tied values, a per-head norm or a rotation with an amplitude")
+            self.rotate_then_norm = False
         if self.rotate_then_norm and (spec.tied_values or spec.qk_norm is not None):
             raise ValueError("tied values and a weighted norm before the rotation are not combined with a norm "
                              "after the rotation, an amplitude or a value size of its own")
+        self.bias: torch.Tensor = None
+        self.sink: torch.Tensor = None
+        self.gate_columns = 0
 
     # ---- weights
     def expected_tensors(self) -> List[TensorSpec]:
@@ -81,14 +100,38 @@ class PagedAttention(Mixer):
         if s.qk_norm is not None:
             out += [TensorSpec(self.names["q_norm"], (s.qk_norm.size,)),
                     TensorSpec(self.names["k_norm"], (s.qk_norm.size,))]
+        if s.biases:
+            out.append(TensorSpec(self.names["q_bias"], (qw,), init=("normal", 0.0, 0.1)))
+            if s.own_kv:
+                out += [TensorSpec(self.names["k_bias"], (kw,), init=("normal", 0.0, 0.1)),
+                        TensorSpec(self.names["v_bias"], (s.num_kv_heads * self.value_dim,), init=("normal", 0.0, 0.1))]
+        if s.whole_norm_eps is not None:
+            out.append(TensorSpec(self.names["q_norm"], (qw,)))
+            if s.own_kv:
+                out.append(TensorSpec(self.names["k_norm"], (kw,)))
+        if s.output_gate:
+            out.append(TensorSpec(self.names["g_proj"], (s.num_heads * self.value_dim, s.hidden_size)))
+        if s.sink:
+            out.append(TensorSpec(self.names["sink"], (s.num_heads,), init=("normal", 0.0, 1.0)))
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         roles = ("q_proj", "k_proj") if self.spec.tied_values else ("q_proj", "k_proj", "v_proj")
         if not self.spec.own_kv:
             roles = ("q_proj",)
+        if self.spec.output_gate:
+            roles = roles + ("g_proj",)
+            self.gate_columns = tensors[self.names["g_proj"]].shape[0]
         mats = [tensors[self.names[r]] for r in roles]
         self.qkv = torch.cat([m.to(mats[0].dtype) for m in mats], dim=0).contiguous()
+        if self.spec.sink:
+            self.sink = tensors[self.names["sink"]].float().contiguous()
+        if self.spec.biases:
+            parts = ("q_bias", "k_bias", "v_bias") if self.spec.own_kv else ("q_bias",)
+            self.bias = torch.cat([tensors[self.names[r]].float() for r in parts]).contiguous()
+        if self.spec.whole_norm_eps is not None:
+            self.q_norm = tensors[self.names["q_norm"]].float().contiguous()
+            self.k_norm = tensors[self.names["k_norm"]].float().contiguous() if self.spec.own_kv else None
         if self.spec.distance_bias is not None:
             self.distance_r1 = tensors[self.names["distance_r1"]].float().contiguous()
             self.distance_r2 = tensors[self.names["distance_r2"]].float().contiguous()
@@ -102,7 +145,8 @@ class PagedAttention(Mixer):
 
     def cache_need(self):
         s = self.spec
-        return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window,
+        kept = s.window if isinstance(s.cache_window, str) else s.cache_window
+        return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=kept,
                            tied_values=s.tied_values,
                            value_dim=self.value_dim if self.value_dim != s.head_dim else None)
 
@@ -126,10 +170,12 @@ class PagedAttention(Mixer):
         writes = cache.writes
         if writes and not s.own_kv:
             raise ValueError("a layer without key and value projections must read another run step's cache")
+        if self.bias_norm_gate:
+            return self._bias_norm_gate_attend(x, residual, ctx, cache)
         if self.rotate_then_norm:
             return self._rotate_norm_attend(x, residual, ctx, cache)
         width = qw + self.kv_arrays * kw if writes else qw
-        modified = s.softcap is not None or s.distance_bias is not None or s.chunk is not None
+        modified = s.softcap is not None or s.distance_bias is not None or s.chunk is not None or s.sink
         fused = self.position.fused_rotation()
         if fused is not None and fused[0] is not None and self._heads_from_the_product(x, ctx, cache, fused):
             return self._attend(residual, ctx, cache)
@@ -203,7 +249,30 @@ class PagedAttention(Mixer):
                               ctx.seq_rows)
         return self._attend(residual, ctx, cache)
 
-    def _attend(self, residual, ctx, cache):
+    def _bias_norm_gate_attend(self, x, residual, ctx, cache):
+        """q | k | v | gate from one product; biases, the norm over the whole q and k,
+        a rotation if the encoding has one, and the append in one kernel; attention;
+        the heads times sigmoid(gate); the output product."""
+        s, rt = self.spec, self.runtime
+        k = rt.kernels
+        T = x.shape[0]
+        nq, nkv, d, dv = s.num_heads, s.num_kv_heads, s.head_dim, self.value_dim
+        writes = cache.writes
+        inv_freq, rotary_dim = self.position.fused_rotation() or (None, 0)
+        if inv_freq is None and s.position.kind != "none":
+            raise ValueError("biases, a whole norm or an output gate need a rotation that the kernels apply")
+        proj = ctx.workspace.get("attn.qkv", (T, self.qkv.shape[0]), rt.dtype)
+        k.linear(x, self.qkv, proj)
+        q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
+        k.qkv_bias_norm_append(proj, q, cache.keys if writes else None, cache.values if writes else None, self.bias,
+                               self.q_norm, self.k_norm, s.whole_norm_eps, inv_freq,
+                               rotary_dim if inv_freq is not None else 0, ctx.positions, ctx.seq_of_token,
+                               ctx.tables[cache.group] if writes else None, nq, nkv, d, dv, cache.page_size,
+                               ctx.seq_rows)
+        gate = proj[:, proj.shape[1] - self.gate_columns:] if self.gate_columns else None
+        return self._attend(residual, ctx, cache, gate)
+
+    def _attend(self, residual, ctx, cache, gate=None):
         """Attention over the cache from the step's q, then the output product, left
         for the next norm to add into the residual."""
         s, rt = self.spec, self.runtime
@@ -220,9 +289,13 @@ class PagedAttention(Mixer):
             extra["chunk"] = s.chunk
         if self.value_dim != d:
             extra["value_dim"] = self.value_dim
+        if s.sink:
+            extra["sink"] = self.sink
         k.attention(q, cache.keys, cache.values, att, ctx.tables[cache.group], ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
                     s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows, **extra)
+        if gate is not None:
+            k.sigmoid_gate(att, gate)
         return k.linear(att, self.o_proj, residual, residual=residual, defer=True)
 
     def _heads_from_the_product(self, x, ctx, cache, fused) -> bool:

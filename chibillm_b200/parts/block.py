@@ -11,14 +11,21 @@ optional per-layer token input (parts/token_input.py).  The branches add into a
 32-bit array of their own; one kernel at the layer's end adds it to the residual
 with the scale, applies the token input and, when the next block's norm asks for
 it, writes that norm's output too (the block leaves that kernel pending, as a
-product is left pending by the other arrangement)."""
+product is left pending by the other arrangement).
+
+"postnorm": the sublayers read the residual itself and the norms sit on their
+outputs, residual += norm(mixer(residual)), then residual += norm(ff(residual)),
+then the optional token input.  With ``token_shift`` the mixer reads every token
+moved towards the one before it, h + (h' - h) * w; the last token's h is kept per
+request (a second cache need of the block, 32-bit), so a portion of a prompt goes
+on where the one before stopped."""
 from __future__ import annotations
 
 from typing import Dict, List
 
 import torch
 
-from .base import (Block, Runtime, TensorSpec, make_feed_forward, make_mixer, make_norm,
+from .base import (Block, FixedStateNeed, Runtime, TensorSpec, make_feed_forward, make_mixer, make_norm,
                    register_block)
 from .short_conv import ShortConv
 from .token_input import TokenInput
@@ -161,5 +168,91 @@ class ParallelBlock(Block):
         return LayerEnd(self, delta, ctx)
 
 
+class PostNormBlock(Block):
+    def __init__(self, layer, runtime: Runtime):
+        if layer.mixer_conv is not None:
+            raise ValueError("the postnorm arrangement has no convolution")
+        self.layer = layer
+        self.runtime = runtime
+        names = {role: layer.weight_prefix + name for role, name in layer.names().items()}
+        self.hidden = layer.mixer_norm.size
+        self.mixer_norm = make_norm(layer.mixer_norm, names["mixer_norm"], runtime)
+        self.mixer = make_mixer(layer.mixer, names, runtime)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = make_norm(layer.feed_forward_norm, names["feed_forward_norm"], runtime)
+            self.feed_forward = make_feed_forward(layer.feed_forward, names, runtime)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "add_to"):
+                raise ValueError(f"norm kind '{norm.spec.kind}' cannot add its output to the residual")
+        self.token_input = None if layer.token_input is None else TokenInput(layer.token_input, names, runtime)
+        self.shift_name = names["token_shift"] if layer.token_shift else None
+        self.shift: torch.Tensor = None
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward,
+                                        self.token_input) if p is not None)
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        out: List[TensorSpec] = []
+        for p in self._parts:
+            out.extend(p.expected_tensors())
+        if self.shift_name is not None:
+            out.append(TensorSpec(self.shift_name, (self.hidden,), init=("uniform", 0.0, 1.0)))
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self._parts:
+            p.bind(tensors)
+        if self.shift_name is not None:
+            self.shift = tensors[self.shift_name].float().contiguous()
+
+    def cache_need(self):
+        if self.shift_name is None:
+            return self.mixer.cache_need()
+        return (self.mixer.cache_need(), FixedStateNeed((("last_input", (self.hidden,), torch.float32),)))
+
+    def launch_key(self, ctx):
+        keys = [p.launch_key(ctx) for p in (self.mixer, self.feed_forward, self.token_input) if p is not None]
+        return None if any(k is None for k in keys) else tuple(keys)
+
+    def forward(self, residual: torch.Tensor, ctx, cache, pending=None):
+        rt = self.runtime
+        k = rt.kernels
+        if pending is not None:
+            pending.add_into(residual)
+        shape = tuple(residual.shape)
+        h = ctx.workspace.get("block.normed", shape, rt.dtype)
+        if self.shift_name is not None:
+            cache, kept = cache
+            k.token_shift(residual, self.shift, kept.arrays["last_input"], ctx.q_start, ctx.seq_of_token,
+                          ctx.state_slots, h)
+        else:
+            k.cast(residual, h)
+        delta = ctx.workspace.get("block.delta", shape, torch.float32)
+        k.zero(delta)
+        left = self.mixer.forward(h, delta, ctx, cache)
+        if left is not None:
+            left.add_into(delta)
+        ti = self.token_input
+        products = ti is not None and ti.wants_products(shape[0])
+        # the residual in the activations' type, for whoever reads it next
+        x = ctx.workspace.get("block.x", shape, rt.dtype)
+        ff = self.feed_forward
+        self.mixer_norm.add_to(delta, residual, copy_out=x if (ff is not None or products) else None)
+        if ff is not None:
+            k.zero(delta)
+            left = ff.forward(x, delta, ctx)
+            if left is not None:
+                left.add_into(delta)
+            self.feed_forward_norm.add_to(delta, residual, copy_out=x if products else None)
+        if ti is not None:
+            side = ti.kernel_arguments(ctx)
+            if products:
+                k.layer_end(residual, None, 1.0, side=side, y_in=ti.products(x, ctx))
+            else:
+                k.layer_end(residual, None, 1.0, side=side)
+        return None
+
+
 register_block("prenorm", PreNormBlock, replace=True)
+register_block("postnorm", PostNormBlock, replace=True)
 register_block("parallel", ParallelBlock, replace=True)

@@ -9,7 +9,13 @@ and multiplies.
 from a table by the token's id; the output is the mean of the chosen experts'.
 All experts' matrices are stacked, the (token, choice) pairs are sorted by
 expert on the device, and two products over tiles of one expert's rows do the
-work; nothing is read on the host, so a decode step can be captured."""
+work; nothing is read on the host, so a decode step can be captured.
+
+"routed_experts": small feed-forwards without a gate, down(act(up(x))), chosen per
+token by a router: the ``top`` largest of z = W_router x (32-bit), weighted by the
+softmax over the chosen logits.  One kernel picks and weighs, the pairs are sorted
+by expert on the device by the kernel that sorts a table's choices, and the same
+two products over tiles of one expert's rows do the work."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -253,6 +259,62 @@ class TableExperts(FeedForward):
         return None
 
 
+class RoutedExperts(FeedForward):
+    ACTIVATIONS = ("relu2", "relu", "silu", "gelu", "gelu_tanh")
+
+    def __init__(self, spec, names: Dict[str, str], runtime: Runtime):
+        if spec.activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation '{spec.activation}' is not supported by routed_experts")
+        if not (0 < spec.top <= spec.num_experts):
+            raise ValueError("routed_experts: 0 < top <= num_experts is required")
+        self.spec = spec
+        self.names = names
+        self.runtime = runtime
+        self.router: torch.Tensor = None        # [experts, hidden]
+        self.up: torch.Tensor = None            # [experts, ff, hidden]
+        self.down: torch.Tensor = None          # [experts, hidden, ff]
+
+    def _name(self, role: str, e: int) -> str:
+        return self.names[role].replace("{e}", str(e))
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        s = self.spec
+        out = [TensorSpec(self.names["router"], (s.num_experts, s.hidden_size), init=("normal", 0.0, 0.5))]
+        for e in range(s.num_experts):
+            out += [TensorSpec(self._name("expert_up", e), (s.intermediate_size, s.hidden_size)),
+                    TensorSpec(self._name("expert_down", e), (s.hidden_size, s.intermediate_size))]
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.router = tensors[self.names["router"]].contiguous()
+        first = tensors[self._name("expert_up", 0)]
+        self.up = torch.stack([tensors[self._name("expert_up", e)].to(first.dtype) for e in range(s.num_experts)])
+        self.down = torch.stack([tensors[self._name("expert_down", e)].to(first.dtype) for e in range(s.num_experts)])
+        self.up, self.down = self.up.contiguous(), self.down.contiguous()
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        s, rt = self.spec, self.runtime
+        k = rt.kernels
+        T = x.shape[0]
+        pairs = T * s.top
+        logits = ctx.workspace.get("router.logits", (T, s.num_experts), torch.float32)
+        k.linear(x, self.router, logits)
+        chosen = ctx.workspace.get("router.chosen", (T, s.top), torch.int32)
+        share = ctx.workspace.get("router.share", (T, s.top), torch.float32)
+        k.router_top(logits, chosen, share)
+        route = ctx.workspace.get("experts.route", (k.route_words(pairs, s.num_experts),), torch.int32)
+        act = ctx.workspace.get("experts.act", (pairs, s.intermediate_size), rt.dtype)
+        y = ctx.workspace.get("experts.out", (pairs, s.hidden_size), torch.float32)
+        sorted_x = ctx.workspace.get("experts.sorted", (pairs, s.hidden_size), rt.dtype)
+        k.chosen_experts(x, chosen, share, self.up, self.down, residual, route, act, y, s.activation, sorted_x)
+        return None
+
+
 register_feed_forward("gated_mlp", GatedMLP, replace=True)
+register_feed_forward("routed_experts", RoutedExperts, replace=True)
 register_feed_forward("table_experts", TableExperts, replace=True)
 register_feed_forward("mlp", DenseMLP, replace=True)

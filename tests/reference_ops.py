@@ -88,7 +88,7 @@ class ReferenceKernels:
 
     def attention(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token,
                   positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0,
-                  seq_rows=None, softcap=None, distance_bias=None, chunk=None, value_dim=None):
+                  seq_rows=None, softcap=None, distance_bias=None, chunk=None, value_dim=None, sink=None):
         self._count("attention")
         T = q.shape[0]
         group = nq // nkv
@@ -116,7 +116,10 @@ class ReferenceKernels:
                 if distance_bias is not None:
                     r1, r2 = distance_bias
                     sc = sc - r1[h].float() * torch.log1p(r2[h].float() * (p - idx).float())
-                pr = torch.softmax(sc, dim=0)
+                if sink is not None:
+                    pr = torch.softmax(torch.cat([sc, sink[h].float().reshape(1)]), dim=0)[:-1]
+                else:
+                    pr = torch.softmax(sc, dim=0)
                 res[t, h] = pr @ vals[:, g, :]
         out.copy_(res.reshape(T, nq * dv).to(out.dtype))
 
@@ -204,6 +207,134 @@ class ReferenceKernels:
         if copy_out is not None:
             copy_out.copy_(residual.to(copy_out.dtype))
 
+    # ---- the operations of mixer_ops.cu
+    def norm_rows(self, y, weight, bias, eps, offset, centered, residual=None, out=None):
+        self._count("norm_rows")
+        v = y.float()
+        if centered:
+            v = v - v.mean(-1, keepdim=True)
+        v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * (weight.float() + offset)
+        if bias is not None:
+            v = v + bias.float()
+        if residual is not None:
+            residual.add_(v)
+            v = residual
+        if out is not None:
+            out.copy_(v.to(out.dtype))
+
+    def token_shift(self, residual, mix, state, q_start, seq_of_token, state_slots, out):
+        self._count("token_shift")
+        starts = q_start.tolist()
+        for s in range(len(starts) - 1):
+            a, b = starts[s], starts[s + 1]
+            if a == b:
+                continue
+            slot = int(state_slots[s])
+            x = residual[a:b]
+            before = torch.cat([state[slot][None, :], x[:-1]], dim=0)
+            out[a:b] = (x + (before - x) * mix.float()).to(out.dtype)
+            state[slot] = x[-1]
+
+    @staticmethod
+    def _rotate_front(x, positions, inv_freq, rot):
+        if not rot:
+            return x
+        half = rot // 2
+        angle = positions.float()[:, None] * inv_freq[:half].float()[None, :]
+        c, s = torch.cos(angle), torch.sin(angle)
+        while c.dim() < x.dim():
+            c, s = c[:, None], s[:, None]
+        lo, hi = x[..., :half], x[..., half:rot]
+        return torch.cat([lo * c - hi * s, hi * c + lo * s, x[..., rot:]], dim=-1)
+
+    def latent_prepare(self, proj, cq, k_cache, q_norm, kv_norm, eps, inv_freq, q_rank, kv_rank, rot, positions,
+                       seq_of_token, block_table, page_size, seq_rows=None):
+        self._count("latent_prepare")
+        p = proj.float()
+        a = p[:, :q_rank]
+        cq.copy_((a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps) * q_norm.float()).to(cq.dtype))
+        if k_cache is None:
+            return
+        c = p[:, q_rank:q_rank + kv_rank]
+        c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * kv_norm.float()
+        shared = self._rotate_front(p[:, q_rank + kv_rank:q_rank + kv_rank + rot], positions, inv_freq, rot)
+        pos = positions.long()
+        rows = seq_of_token.long() if seq_rows is None else seq_rows.long()[seq_of_token.long()]
+        pages = block_table[rows, pos // page_size].long()
+        assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "append outside the pool"
+        k_cache[pages, 0, pos % page_size, :] = torch.cat([shared, c], dim=-1).to(k_cache.dtype)
+
+    def qkv_bias_norm_append(self, proj, q_out, k_cache, v_cache, bias, q_norm, k_norm, eps, inv_freq, rot, positions,
+                             seq_of_token, block_table, nq, nkv, d, dv, page_size, seq_rows=None):
+        self._count("qkv_bias_norm_append")
+        T = proj.shape[0]
+        qw, kw, vw = nq * d, nkv * d, nkv * dv
+        append = k_cache is not None
+        width = qw + (kw + vw if append else 0)
+        p = proj[:, :width].float()
+        if bias is not None:
+            p = p + bias.float()[:width]
+
+        def whole(x, w):
+            if w is None:
+                return x
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+
+        q = self._rotate_front(whole(p[:, :qw], q_norm).reshape(T, nq, d), positions, inv_freq, rot)
+        q_out.copy_(q.reshape(T, qw).to(q_out.dtype))
+        if not append:
+            return
+        kk = self._rotate_front(whole(p[:, qw:qw + kw], k_norm).reshape(T, nkv, d), positions, inv_freq, rot)
+        v = p[:, qw + kw:].reshape(T, nkv, dv)
+        pos = positions.long()
+        rows = seq_of_token.long() if seq_rows is None else seq_rows.long()[seq_of_token.long()]
+        pages = block_table[rows, pos // page_size].long()
+        assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "append outside the pool"
+        k_cache[pages, :, pos % page_size, :] = kk.to(k_cache.dtype)
+        v_cache[pages, :, pos % page_size, :] = v.to(v_cache.dtype)
+
+    def sigmoid_gate(self, x, gate):
+        self._count("sigmoid_gate")
+        x.copy_((x.float() * torch.sigmoid(gate.float())).to(x.dtype))
+
+    def recurrence_gates(self, proj, bias, floor, qf, kw):
+        self._count("recurrence_gates")
+        q = proj[:, :kw].float()
+        qf[:, :kw] = q * torch.sigmoid(q)
+        qf[:, kw:] = floor + (1.0 - floor) * torch.sigmoid(proj[:, kw:2 * kw].float() + bias)
+
+    def gated_recurrence(self, qf, v, state, o, q_start, state_slots, heads, d, e, max_q_len):
+        self._count("gated_recurrence")
+        starts = q_start.tolist()
+        kw = heads * d
+        for s in range(len(starts) - 1):
+            slot = int(state_slots[s])
+            S = state[slot]
+            for t in range(starts[s], starts[s + 1]):
+                q = qf[t, :kw].view(heads, d)
+                f = qf[t, kw:].view(heads, d)
+                vt = v[t].float().view(heads, e)
+                S = f[:, :, None] * S + (1.0 - f)[:, :, None] * vt[:, None, :]
+                o[t] = torch.einsum("hde,hd->he", S, q).reshape(-1)
+            state[slot] = S
+
+    def router_top(self, logits, chosen, share):
+        self._count("router_top")
+        top = chosen.shape[1]
+        best, idx = torch.topk(logits, top, dim=-1)
+        chosen.copy_(idx.to(chosen.dtype))
+        share.copy_(torch.softmax(best, dim=-1))
+
+    def chosen_experts(self, x, chosen, share, up, down, acc, route, act, y, kind, sorted_x=None):
+        self._count("chosen_experts")
+        for t in range(x.shape[0]):
+            total = torch.zeros_like(acc[t])
+            for s in range(chosen.shape[1]):
+                e = int(chosen[t, s])
+                hidden = self._act(up[e].float() @ x[t].float(), kind).to(x.dtype).float()
+                total += share[t, s] * (down[e].float() @ hidden)
+            acc[t] += total
+
     def side_gate(self, gate, tokens, table, offset, kind):
         e = table[tokens.long(), offset:offset + gate.shape[1]].float()
         gate.copy_((self._act(gate.float(), kind) * e).to(gate.dtype))
@@ -250,6 +381,8 @@ class ReferenceKernels:
             y = z / (1.0 + torch.exp(-z))
         elif kind == "relu":
             y = torch.clamp(z, min=0.0)
+        elif kind == "relu2":
+            y = torch.clamp(z, min=0.0) ** 2
         elif kind == "tanh":
             y = torch.tanh(z)
         else:
