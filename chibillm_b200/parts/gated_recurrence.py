@@ -2,8 +2,8 @@
 which the forget gate also decides what is written.
 
 One product gives q | f | v for all heads.  A first kernel makes the recurrence's
-inputs in 32-bit: silu(q) and the gate f = l + (1 - l) * sigmoid(f + b) with its
-lower bound l per channel.  The recurrence kernel then runs, per head,
+inputs in 32-bit: silu(q), the gate f = l + (1 - l) * sigmoid(f + b) with its
+lower bound l per channel, and v.  The recurrence kernel then runs, per head,
 
     S <- diag(f) S + (1 - f) v^T,   o = S^T q
 
@@ -66,11 +66,11 @@ class GatedRecurrence(Mixer):
         kw, vw = s.num_heads * s.head_dim, s.num_heads * s.value_dim
         proj = ctx.workspace.get("recurrence.proj", (T, 2 * kw + vw), rt.dtype)
         k.linear(x, self.stacked, proj)
-        qf = ctx.workspace.get("recurrence.qf", (T, 2 * kw), torch.float32)
-        k.recurrence_gates(proj, self.gate_bias, self.gate_floor, qf, kw)
+        qfv = ctx.workspace.get("recurrence.qfv", (T, 2 * kw + vw), torch.float32)
+        k.recurrence_gates(proj, self.gate_bias, self.gate_floor, qfv, kw)
         o = ctx.workspace.get("recurrence.o", (T, vw), torch.float32)
-        k.gated_recurrence(qf, proj[:, 2 * kw:], cache.arrays["state"], o, ctx.q_start, ctx.state_slots,
-                           s.num_heads, s.head_dim, s.value_dim, ctx.max_q_len)
+        k.gated_recurrence(qfv, cache.arrays["state"], o, ctx.q_start, ctx.state_slots, s.num_heads, s.head_dim,
+                           s.value_dim, ctx.max_q_len)
         normed = ctx.workspace.get("recurrence.normed", (T, vw), rt.dtype)
         k.rmsnorm(o.view(-1, s.value_dim), self.norm_weight, s.norm_eps, 0.0, normed.view(-1, s.value_dim))
         return k.linear(normed, self.o_proj, residual, residual=residual, defer=True)

@@ -297,13 +297,14 @@ class ReferenceKernels:
         self._count("sigmoid_gate")
         x.copy_((x.float() * torch.sigmoid(gate.float())).to(x.dtype))
 
-    def recurrence_gates(self, proj, bias, floor, qf, kw):
+    def recurrence_gates(self, proj, bias, floor, out, kw):
         self._count("recurrence_gates")
         q = proj[:, :kw].float()
-        qf[:, :kw] = q * torch.sigmoid(q)
-        qf[:, kw:] = floor + (1.0 - floor) * torch.sigmoid(proj[:, kw:2 * kw].float() + bias)
+        out[:, :kw] = q * torch.sigmoid(q)
+        out[:, kw:2 * kw] = floor + (1.0 - floor) * torch.sigmoid(proj[:, kw:2 * kw].float() + bias)
+        out[:, 2 * kw:] = proj[:, 2 * kw:].float()
 
-    def gated_recurrence(self, qf, v, state, o, q_start, state_slots, heads, d, e, max_q_len):
+    def gated_recurrence(self, qfv, state, o, q_start, state_slots, heads, d, e, max_q_len=0):
         self._count("gated_recurrence")
         starts = q_start.tolist()
         kw = heads * d
@@ -311,9 +312,9 @@ class ReferenceKernels:
             slot = int(state_slots[s])
             S = state[slot]
             for t in range(starts[s], starts[s + 1]):
-                q = qf[t, :kw].view(heads, d)
-                f = qf[t, kw:].view(heads, d)
-                vt = v[t].float().view(heads, e)
+                q = qfv[t, :kw].view(heads, d)
+                f = qfv[t, kw:2 * kw].view(heads, d)
+                vt = qfv[t, 2 * kw:].view(heads, e)
                 S = f[:, :, None] * S + (1.0 - f)[:, :, None] * vt[:, None, :]
                 o[t] = torch.einsum("hde,hd->he", S, q).reshape(-1)
             state[slot] = S
