@@ -1,5 +1,5 @@
 // Causal grouped-query attention over the paged cache, any head size up to
-// 256, any group size, optional window; element types are template parameters.
+// 1,024, any group size, optional window; element types are template parameters.
 //
 // This is the attention of the true 32-bit path and the fall-back of the
 // bfloat16 path for head sizes the tensor-core kernels do not cover.  One warp
@@ -25,9 +25,9 @@
 
 namespace chibi {
 
-constexpr int MAX_D = 256;
+constexpr int MAX_D = 1024;      // head sizes up to 256 keep 8 sums per lane, larger ones 32
 
-template <typename TQ, typename TC>
+template <typename TQ, typename TC, int SLOTS>
 __global__ void __launch_bounds__(128)
 attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
                          const TC* __restrict__ v_cache, TQ* __restrict__ out,
@@ -60,7 +60,6 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
     const int first = first_visible_key(pos, window, chunk);
     const float r1 = bias_r1 ? bias_r1[head] : 0.f, r2 = bias_r1 ? bias_r2[head] : 0.f;
     const int* table = block_table + (size_t)(seq_rows ? seq_rows[seq] : seq) * table_stride;
-    constexpr int SLOTS = MAX_D / 32;
     float acc[SLOTS];
 #pragma unroll
     for (int i = 0; i < SLOTS; ++i)
@@ -153,10 +152,16 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
         return CHIBI_ERR_UNSUPPORTED;
     const size_t smem = (size_t)warps * d * sizeof(float);
     CHIBI_DISPATCH_TYPE(q_type, TQ, CHIBI_DISPATCH_TYPE(cache_type, TC, {
-        launch(attention_generic_kernel<TQ, TC>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 
-            (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
-            table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, dv, page_size,
-            num_pages, scale, window, chunk, softcap, bias_r1, bias_r2, sink, error);
+        if (dv <= 256)
+            launch(attention_generic_kernel<TQ, TC, 8>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream,
+                (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
+                table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, dv, page_size,
+                num_pages, scale, window, chunk, softcap, bias_r1, bias_r2, sink, error);
+        else
+            launch(attention_generic_kernel<TQ, TC, MAX_D / 32>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream,
+                (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
+                table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, dv, page_size,
+                num_pages, scale, window, chunk, softcap, bias_r1, bias_r2, sink, error);
     }));
     return launch_status();
 }

@@ -75,8 +75,16 @@ struct AttnParams {
     const float* bias_r1;          // [nq] or null
     const float* bias_r2;
     int tied;                      // the values are the keys: one tile serves both
+    const float* sink;             // [nq] or null: exp(sink[head]) joins the softmax's denominator, once
     int* error;
 };
+
+// What the sink adds to a row's sum of weights, which is kept relative to the running maximum
+// `m` (in units of log2; -inf while no key has been seen, then the sum is relative to 0).
+__device__ __forceinline__ float sink_weight(const float* sink, int head, float m)
+{
+    return sink ? exp2f(sink[head] * 1.4426950408889634f - (m == -INFINITY ? 0.f : m)) : 0.f;
+}
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid)
 {
@@ -611,6 +619,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         }
         const int head = head0 + row;
         if (p.splits == 1) {
+            lsum += sink_weight(p.sink, head, mmax);
             p.out[((size_t)t * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
         } else {
             const size_t slot = ((size_t)seq * p.nq + head) * p.splits + split;
@@ -660,6 +669,7 @@ __global__ void attn_decode_merge_kernel(const AttnParams p)
         }
         m_run = m_new;
     }
+    lsum += sink_weight(p.sink, head, m_run);
     p.out[((size_t)t * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
 }
 
@@ -784,6 +794,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
         if (r >= rows_total)
             continue;
         const int tok = r / p.group, head = kv_head * p.group + (r - tok * p.group);
+        l[h] += sink_weight(p.sink, head, m[h]);
         const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
         __nv_bfloat16* dst = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
 #pragma unroll
@@ -813,7 +824,8 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
                                   const int* q_start, const int* ctx_len, int seqs, int nq, int nkv, int page_size,
                                   int num_pages, float scale, int window, int chunk, int mode, int max_q_len,
                                   int splits, float* scratch, long long scratch_floats, float softcap,
-                                  const float* bias_r1, const float* bias_r2, int* error, cudaStream_t stream)
+                                  const float* bias_r1, const float* bias_r2, const float* sink, int* error,
+                                  cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
@@ -845,6 +857,7 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
     p.softcap = softcap;
     p.bias_r1 = bias_r1;
     p.bias_r2 = bias_r2;
+    p.sink = sink;
     p.tied = k_cache == v_cache ? 1 : 0;
     static bool configured = false;
     if (!configured) {

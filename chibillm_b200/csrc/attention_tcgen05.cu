@@ -79,7 +79,15 @@ struct AttnTcParams {
     int kv_splits;                 // 1: none
     float* part_o;                 // [tokens][nq][kv_splits][D]
     float* part_ml;                // [tokens][nq][kv_splits][2]
+    const float* sink;             // [nq] or null: exp(sink[head]) joins the softmax's denominator, once
 };
+
+// What the sink adds to a row's sum of weights, which is kept relative to the running maximum
+// `m` (in units of log2; -inf while no key has been seen, then the sum is relative to 0).
+__device__ __forceinline__ float sink_weight(const float* sink, int head, float m)
+{
+    return sink ? exp2f(sink[head] * 1.4426950408889634f - (m == -INFINITY ? 0.f : m)) : 0.f;
+}
 
 // Byte offset of element (row, col) of a [rows][64] bf16 tile laid out with the
 // 128-byte swizzle (what TMA writes and tcgen05.mma reads): 16-byte chunk c of
@@ -453,6 +461,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 p.part_ml[slot * 2 + 1] = l;
             }
         } else {
+        l += sink_weight(p.sink, head, m);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         __nv_bfloat16* dst_row = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
 #pragma unroll
@@ -520,6 +529,7 @@ __global__ void attn_prefill_merge_kernel(const AttnTcParams p)
         }
         m_run = m_new;
     }
+    lsum += sink_weight(p.sink, head, m_run);
     p.out[((size_t)(t0 + blockIdx.y) * p.nq + head) * D + c] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
 }
 
@@ -897,6 +907,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             mbar_wait(&o_done[q], (my_tiles - 1) & 1, p.error, 48);
             tcgen05_fence_after();
             const int head = kv_head * p.group + (r - tok * p.group);
+            l += sink_weight(p.sink, head, m);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* dst_row = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
 #pragma unroll
@@ -943,7 +954,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
                                          int skip_single, int max_q_len, int variant, int kv_splits,
                                          float* scratch, long long scratch_floats, long long tokens,
                                          float softcap, const float* bias_r1, const float* bias_r2,
-                                         int* error, cudaStream_t stream)
+                                         const float* sink, int* error, cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
@@ -979,6 +990,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     p.softcap = softcap;
     p.bias_r1 = bias_r1;
     p.bias_r2 = bias_r2;
+    p.sink = sink;
     const bool with_options = softcap > 0.f || bias_r1 != nullptr;
     CUtensorMap mk, mv;
     if (!tensor_map_2d(k_cache, p.cache_rows, D, D, page_size, &mk)

@@ -10,9 +10,10 @@
 // tcgen05.ld.  Rows past the expert's last row are computed (they are the next expert's
 // rows, or zeros past the array's end) and not written.
 //
-// GATED: an expert's matrix holds blocks of 16 gate rows followed by their 16 up rows, so
-// 32 accumulator columns are 16 gate sums and their 16 up sums; out[r, f] = act(gate) * up
-// in bfloat16.  Otherwise out is 32-bit [pairs, rows_w].
+// MODE 1 (gated): an expert's matrix holds blocks of 16 gate rows followed by their 16 up rows,
+// so 32 accumulator columns are 16 gate sums and their 16 up sums; out[r, f] = act(gate) * up
+// in bfloat16.  MODE 2: out[r, n] = act(sum) in bfloat16 (an expert without a gate).
+// MODE 0: out is 32-bit [pairs, rows_w].
 //
 // Warp roles (192 threads): warp 0 loads, warp 1 owns TMEM and issues, warps 2..5 are the
 // epilogue (warp w reads TMEM lanes 32 * (w % 4) ..).  Every wait has a limit; a wait that
@@ -43,7 +44,7 @@ struct ExpertTileParams {
     int* error;
 };
 
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(XT_THREADS)
 expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const ExpertTileParams p)
@@ -131,7 +132,29 @@ expert_rows_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tmem_load_wait();
             if (!write)
                 continue;
-            if (GATED) {
+            if (MODE == 2) {
+                if (n0 + c0 >= p.rows_w)
+                    continue;
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)r * p.out_stride + n0 + c0;
+                __nv_bfloat162 h[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    h[j] = __floats2bfloat162_rn(activate(__uint_as_float(v[2 * j]), p.kind),
+                                                 activate(__uint_as_float(v[2 * j + 1]), p.kind));
+                if (n0 + c0 + 32 <= p.rows_w && p.out_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<uint4*>(h)[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (n0 + c0 + 2 * j < p.rows_w)
+                            dst[2 * j] = h[j].x;
+                        if (n0 + c0 + 2 * j + 1 < p.rows_w)
+                            dst[2 * j + 1] = h[j].y;
+                    }
+                }
+            } else if (MODE == 1) {
                 const int col = (n0 + c0) / 2;          // 32 accumulator columns = 16 features
                 if (col >= p.rows_w / 2)
                     continue;
@@ -182,8 +205,8 @@ using namespace chibi;
 
 // One product of the routed rows on tcgen05.  a: [pairs, K] bfloat16, contiguous, sorted by expert;
 // w: [experts, rows_w, K] bfloat16, contiguous (gated: rows_w = 2 F, interleaved in blocks of 16);
-// route: as route_by_table lays it out for tiles of 128 rows.  out: gated: bfloat16 [pairs, F] with
-// out_stride; else float [pairs, rows_w].  CHIBI_ERR_UNSUPPORTED for sizes it does not take.
+// route: as route_by_table lays it out for tiles of 128 rows.  out: gated == 1: bfloat16 [pairs, F]
+// with out_stride; gated == 2: bfloat16 [pairs, rows_w], act(sum); else float [pairs, rows_w].  CHIBI_ERR_UNSUPPORTED for sizes it does not take.
 CHIBI_API int chibi_expert_rows_tc(const void* a, const void* w, void* out, long long out_stride, const int* route,
                                    long long pairs, int experts, int rows_w, int K, int gated, int kind, int* error,
                                    cudaStream_t stream)
@@ -192,7 +215,7 @@ CHIBI_API int chibi_expert_rows_tc(const void* a, const void* w, void* out, long
         return CHIBI_OK;
     if (!a || !w || !out || !route || experts <= 0 || rows_w <= 0 || K <= 0)
         return CHIBI_ERR_ARGUMENT;
-    if (K % XT_K != 0 || (gated && rows_w % 32 != 0) || (reinterpret_cast<uintptr_t>(a) & 15)
+    if (K % XT_K != 0 || (gated == 1 && rows_w % 32 != 0) || (reinterpret_cast<uintptr_t>(a) & 15)
         || (reinterpret_cast<uintptr_t>(w) & 15) || pairs > 2147483647LL - XT_M
         || (long long)experts * rows_w > 2147483647LL - XT_N)
         return CHIBI_ERR_UNSUPPORTED;
@@ -215,18 +238,23 @@ CHIBI_API int chibi_expert_rows_tc(const void* a, const void* w, void* out, long
     const dim3 grid((unsigned)((rows_w + XT_N - 1) / XT_N), (unsigned)max_tiles);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(expert_rows_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(expert_rows_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)XT_SMEM);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(expert_rows_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            e = cudaFuncSetAttribute(expert_rows_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)XT_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(expert_rows_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)XT_SMEM);
         if (e != cudaSuccess)
             return (int)e;
         configured = true;
     }
-    if (gated)
-        launch(expert_rows_tc_kernel<true>, grid, dim3(XT_THREADS), XT_SMEM, stream, map_a, map_b, p);
+    if (gated == 1)
+        launch(expert_rows_tc_kernel<1>, grid, dim3(XT_THREADS), XT_SMEM, stream, map_a, map_b, p);
+    else if (gated == 2)
+        launch(expert_rows_tc_kernel<2>, grid, dim3(XT_THREADS), XT_SMEM, stream, map_a, map_b, p);
     else
-        launch(expert_rows_tc_kernel<false>, grid, dim3(XT_THREADS), XT_SMEM, stream, map_a, map_b, p);
+        launch(expert_rows_tc_kernel<0>, grid, dim3(XT_THREADS), XT_SMEM, stream, map_a, map_b, p);
     return launch_status();
 }

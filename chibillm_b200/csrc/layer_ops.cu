@@ -343,8 +343,9 @@ expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int*
 // experts of that size): every block first walks tile map -> offsets -> row index -> row, four dependent
 // trips, for 64 KB of weights; it is not kept.  Rows that a tile does not have are filled with zeros and not
 // stored, so a decode step's tiles of one or two rows stream their expert's weights once.
-// GATED: the expert's matrix holds blocks of 16 gate rows followed by their 16 up rows, so a
+// MODE 1 (gated): the expert's matrix holds blocks of 16 gate rows followed by their 16 up rows, so a
 // warp's 32 columns are 16 gate sums and the 16 up sums that belong to them, in the same lanes.
+// MODE 2: out = act(sum) in bfloat16 (an expert without a gate); MODE 0: the sums in 32-bit.
 constexpr int TG_M = 128, TG_N = 128, TG_K = 32, TG_PAD = 40, TG_STAGES = 4;
 
 __device__ __forceinline__ void tg_cp_async16(void* dst, const void* src, bool valid)
@@ -368,7 +369,7 @@ __device__ __forceinline__ void tg_mma_bf16(float (&c)[4], const uint32_t (&a)[4
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(256, 2)
 expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, const int* __restrict__ a_index,
                        int a_div, const __nv_bfloat16* __restrict__ w, long long w_expert_stride, void* __restrict__ out,
@@ -473,7 +474,17 @@ expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, 
             const int r = row0 + warp_m * 64 + mi * 16 + (lane >> 2) + half * 8;
             if (r >= row_end)
                 continue;
-            if (GATED) {
+            if (MODE == 2) {
+                __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(out) + (size_t)r * out_stride;
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = n0 + warp_n * 32 + ni * 8 + (lane & 3) * 2 + e;
+                        if (col < N)
+                            orow[col] = __float2bfloat16_rn(activate(acc[mi][ni][half * 2 + e], kind));
+                    }
+            } else if (MODE == 1) {
                 __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(out) + (size_t)r * out_stride;
                 const int base = (n0 + warp_n * 32) / 2;
 #pragma unroll
@@ -767,29 +778,20 @@ CHIBI_API int chibi_expert_rows_gemm(const void* a, int a_type, long long a_stri
     const int* tile_expert = pair_of_row + 2 * pairs;
     const int* tile_row0 = tile_expert + max_tiles;
     const long long w_stride = (long long)(gated == 1 ? 2 : 1) * N * K;
-    if (gated == 2 && tile_rows != EG_M)
-        return CHIBI_ERR_UNSUPPORTED;
     if (tile_rows == TG_M) {
         if (a_type != CHIBI_BF16 || w_type != CHIBI_BF16 || K % TG_K != 0 || a_stride % 8 != 0
             || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
-            || (gated && (!interleaved || N % 16 != 0)))
+            || (gated == 1 && (!interleaved || N % 16 != 0)))
             return CHIBI_ERR_UNSUPPORTED;
-        const int rows_of_w = gated ? 2 * N : N;
+        const int rows_of_w = gated == 1 ? 2 * N : N;
         const dim3 tgrid((unsigned)((rows_of_w + TG_N - 1) / TG_N), (unsigned)max_tiles);
         const size_t smem = (size_t)TG_STAGES * (TG_M + TG_N) * TG_PAD * sizeof(__nv_bfloat16);
-        if (gated) {
-            auto kernel = expert_rows_mma_kernel<true>;
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            launch(kernel, tgrid, dim3(256), smem, stream, (const __nv_bfloat16*)a, a_stride,
-                   gather ? pair_of_row : (const int*)nullptr, top, (const __nv_bfloat16*)w, w_stride, out, out_stride,
-                   offsets, tile_expert, tile_row0, rows_of_w, K, kind);
-        } else {
-            auto kernel = expert_rows_mma_kernel<false>;
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            launch(kernel, tgrid, dim3(256), smem, stream, (const __nv_bfloat16*)a, a_stride,
-                   gather ? pair_of_row : (const int*)nullptr, top, (const __nv_bfloat16*)w, w_stride, out, out_stride,
-                   offsets, tile_expert, tile_row0, rows_of_w, K, kind);
-        }
+        auto kernel = gated == 1 ? expert_rows_mma_kernel<1> : gated == 2 ? expert_rows_mma_kernel<2>
+                                                                          : expert_rows_mma_kernel<0>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch(kernel, tgrid, dim3(256), smem, stream, (const __nv_bfloat16*)a, a_stride,
+               gather ? pair_of_row : (const int*)nullptr, top, (const __nv_bfloat16*)w, w_stride, out, out_stride,
+               offsets, tile_expert, tile_row0, rows_of_w, K, kind);
         return launch_status();
     }
     const dim3 grid((unsigned)((N + EG_N - 1) / EG_N), (unsigned)max_tiles);

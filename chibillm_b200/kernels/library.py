@@ -79,11 +79,11 @@ _SIGNATURES = {
     },
     "chibi_attention_tc": {
         "chibi_attention_tc_head_dim": [],
-        "chibi_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, I, P, L, L, F, P, P, P, P],
+        "chibi_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, I, P, L, L, F, P, P, P, P, P],
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],
-        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, L, F, P, P, P, P],
+        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, L, F, P, P, P, P, P],
         "chibi_attention_decode_fused": [P, I, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, P, P,
                                          F, F, I, P, P],
     },

@@ -798,10 +798,10 @@ class CudaKernels:
             raise KernelError(f"attention: cache shapes {tuple(k_cache.shape)} / {tuple(v_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
         if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-                and d % 16 == 0 and d <= 256 and dv == d and sink is None):
+                and d % 16 == 0 and d <= 256 and dv == d):
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                                 page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows, cap, r1, r2,
-                                chunk)
+                                chunk, sink)
             return
         self.launches += 1
         _check(self.lib.chibi_attention_generic(
@@ -854,7 +854,7 @@ class CudaKernels:
 
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                        page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows,
-                       softcap: float = 0.0, bias_r1=None, bias_r2=None, chunk: int = 0) -> None:
+                       softcap: float = 0.0, bias_r1=None, bias_r2=None, chunk: int = 0, sink=None) -> None:
         lib = self._attention_libs.get(d)
         if lib is None:
             lib = self._load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
@@ -880,7 +880,7 @@ class CudaKernels:
                 float(scale), int(window or 0), int(chunk), 1 if mode & 1 else 0, int(max_q_len),
                 int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
                 part.numel() if part is not None else 0, q.shape[0], float(softcap), _ptr(bias_r1), _ptr(bias_r2),
-                _ptr(self.error), self._stream())
+                _ptr(sink), _ptr(self.error), self._stream())
             if status == 0:
                 # (key ranges belong to the kernel with one query tile per CTA, and bring a merge kernel)
                 self.launches += 2 if kv_splits > 1 and self.tcgen05_attention_variant != 2 else 1
@@ -899,7 +899,7 @@ class CudaKernels:
             _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0], float(scale),
             int(window or 0), int(chunk), mode, int(max_q_len), splits, _ptr(scratch),
             scratch.numel() if scratch is not None else 0, float(softcap), _ptr(bias_r1), _ptr(bias_r2),
-            _ptr(self.error), self._stream())
+            _ptr(sink), _ptr(self.error), self._stream())
         self.launches += (1 if mode & 1 else 0) + (1 if mode & 1 and splits > 1 else 0) + (1 if mode & 2 else 0)
         _check(status, "attention (tensor cores)")
 
@@ -1510,15 +1510,41 @@ class CudaKernels:
             raise KernelError("chosen_experts: shapes or types")
         stream = self._stream()
         self.launches += 4
-        tile = self._expert_tile_rows[0]
+        # as ``routed_experts``: bfloat16 experts of sizes that are multiples of 32 run on the tensor cores
+        # (tiles of 128 rows; multiples of 64: tcgen05), everything else the plain kernel
+        fast = up.dtype == torch.bfloat16 and self.expert_tensor_cores(x.dtype, D, F) and x.stride(0) % 8 == 0
+        tile = self._expert_tile_rows[1 if fast else 0]
+        code = self.ACTIVATIONS[kind]
         _check(self.lib.chibi_route_by_table(None, _ptr(chosen), T, top, E, T, tile, _ptr(route), _ptr(self.error),
                                              stream), "chosen_experts (route)")
+        if fast and sorted_x is not None and pairs >= self.EXPERTS_TCGEN05_MIN_PAIRS \
+                and self.experts_on_tcgen05(x.dtype, D, F):
+            _need_cuda(sorted_x)
+            if sorted_x.shape != (pairs, D) or sorted_x.dtype != x.dtype or not sorted_x.is_contiguous() \
+                    or not x.is_contiguous():
+                raise KernelError("chosen_experts: sorted_x is contiguous [T top, D] of x's type")
+            max_tiles = (pairs + tile - 1) // tile + E
+            rows = route[E + 1 + 2 * pairs + 2 * max_tiles:E + 1 + 3 * pairs + 2 * max_tiles]
+            self.gather_rows(x, rows, sorted_x)
+            s1 = self.lib.chibi_expert_rows_tc(_ptr(sorted_x), _ptr(up), _ptr(act), F, _ptr(route), pairs, E, F, D, 2,
+                                               code, _ptr(self.error), stream)
+            if s1 == 0:
+                _check(self.lib.chibi_expert_rows_tc(_ptr(act), _ptr(down), _ptr(y), D, _ptr(route), pairs, E, D, F, 0,
+                                                     0, _ptr(self.error), stream), "chosen_experts (down, tcgen05)")
+                _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
+                                                      1.0, _ptr(share), stream), "chosen_experts (combine)")
+                self.tensor_core_calls += 2
+                return
+            if s1 != -2:
+                _check(s1, "chosen_experts (up, tcgen05)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(x), _code(x), x.stride(0), 1, top, _ptr(up), _code(up), _ptr(act),
-                                               F, _ptr(route), pairs, E, F, D, 2, self.ACTIVATIONS[kind], tile, 0,
-                                               stream), "chosen_experts (up)")
+                                               F, _ptr(route), pairs, E, F, D, 2, code, tile, 0, stream),
+               "chosen_experts (up)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(act), _code(act), F, 0, top, _ptr(down), _code(down), _ptr(y), D,
                                                _ptr(route), pairs, E, D, F, 0, 0, tile, 0, stream),
                "chosen_experts (down)")
+        if fast:
+            self.tensor_core_calls += 2
         _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E, 1.0,
                                               _ptr(share), stream), "chosen_experts (combine)")
 

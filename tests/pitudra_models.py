@@ -8,6 +8,9 @@ rotated parts of 4 to 16 features, windows from one position to longer than any
 test prompt and none at all, readers of another layer's latents with a window
 shorter and longer than their source's, layers without a feed-forward, one to
 three choices out of 3 to 9 experts, with and without the token input.
+The scales and the weights' sizes keep attention scores and router logits within a few units, as a
+trained model's are: scores of 15 or more make single rows of a bfloat16 run depend on the rounding
+of one score (the tests of the kernels alone use such scores on purpose, in both types).
 The weights are made here, with torch's generator, and written with the
 ``safetensors`` library; nothing of the package takes part.
 """
@@ -27,7 +30,7 @@ def moe(ff, experts, top):
 
 def latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, window=None, base=10000.0, scale=None, kv_from=None, mlp=None):
     m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
-         "rot": {"base": base, "dims": rot_dim}, "scale": scale if scale is not None else 1.5 / math.sqrt(dim + rot_dim)}
+         "rot": {"base": base, "dims": rot_dim}, "scale": scale if scale is not None else 0.5 / math.sqrt(dim + rot_dim)}
     if window is not None:
         m["mask"] = {"size": window}
     if kv_from is not None:
@@ -41,7 +44,7 @@ def recurrent(heads, dim, vdim, mlp=None):
 
 def attention(heads, kv_heads, dim, vdim=None, window=None, scale=None, mlp=None):
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim if vdim is None else vdim,
-         "scale": scale if scale is not None else 4.0 / math.sqrt(dim)}
+         "scale": scale if scale is not None else 1.5 / math.sqrt(dim)}
     if window is not None:
         m["mask"] = {"size": window}
     return {"type": "attention", "mixer": m, "mlp": mlp}
@@ -145,7 +148,7 @@ def random_weights(config: dict, seed: int, dtype=torch.bfloat16) -> Dict[str, t
             E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
             w[p + "norm2"] = around_one(D)
             w[p + "norm2.b"] = normal(D, std=0.1)
-            w[p + "mlp.router"] = matrix(E, D, gain=4.0)
+            w[p + "mlp.router"] = matrix(E, D, gain=1.5)
             for n in range(E):
                 w[f"{p}mlp.e{n}.up"] = matrix(ff, D)
                 w[f"{p}mlp.e{n}.down"] = matrix(D, ff, gain=2.0)
@@ -168,9 +171,55 @@ def write_model(config: dict, folder: str, seed: int, dtype=torch.bfloat16, weig
 
 
 def plain_logits(config: dict, seed: int, requests: Dict[str, List[int]], dtype=torch.float64, stored=torch.bfloat16,
-                 weights: Optional[dict] = None) -> Dict[str, torch.Tensor]:
-    """The plain implementation on the weights that ``write_model`` stores."""
+                 weights: Optional[dict] = None, margins: Optional[dict] = None) -> Dict[str, torch.Tensor]:
+    """The plain implementation on the weights that ``write_model`` stores.  ``margins``, a dict,
+    takes per request how close each position's closest call was (see ``plain_pitudra.forward``)."""
     import plain_pitudra
 
     w = random_weights(config, seed, stored) if weights is None else weights
-    return {rid: plain_pitudra.forward(config, w, ids, dtype).float() for rid, ids in requests.items()}
+    out = {}
+    for rid, ids in requests.items():
+        m = None
+        if margins is not None:
+            m = margins[rid] = torch.full((len(ids),), float("inf"), dtype=torch.float64)
+        out[rid] = plain_pitudra.forward(config, w, ids, dtype, margins=m).float()
+    return out
+
+
+def all_experts(config: dict) -> dict:
+    """The same model with every expert chosen by every token: nothing is decided by a comparison
+    of router logits, so that a run in bfloat16 cannot rightly choose other experts than the
+    plain implementation (the weights do not depend on ``top``)."""
+    cfg = json.loads(json.dumps(config))
+    for l in cfg["layers"]:
+        if l.get("mlp") is not None:
+            l["mlp"]["router"]["top"] = l["mlp"]["router"]["experts"]
+    return cfg
+
+
+def safe_prefix(margins: torch.Tensor, least: float) -> int:
+    """How many leading positions of a request have no close call nearer than ``least``; a close
+    call's effect reaches later positions, never earlier ones."""
+    close = torch.nonzero(margins < least)
+    return int(close[0, 0]) if close.numel() else int(margins.numel())
+
+
+# Below these margins a run may rightly decide otherwise than the plain implementation in 64-bit:
+# bfloat16 rounds the router's input to 8 bits, 32-bit runs differ by the order of their sums.
+LEAST_MARGIN = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+def cut_to_safe(got: Dict[str, torch.Tensor], ref: Dict[str, torch.Tensor], margins: Dict[str, torch.Tensor],
+                dtype: str, most_lost: float = 0.4):
+    """Both sets of logits cut to each request's positions before its first close call (requests
+    with none left are dropped); at most ``most_lost`` of all positions may go that way."""
+    a, b, kept, total = {}, {}, 0, 0
+    for rid, r in ref.items():
+        n = safe_prefix(margins[rid], LEAST_MARGIN[dtype])
+        total += r.shape[0]
+        kept += n
+        assert got[rid].shape == r.shape, f"{rid}: shape {tuple(got[rid].shape)} vs {tuple(r.shape)}"
+        if n:
+            a[rid], b[rid] = got[rid][:n], r[:n]
+    assert kept >= (1.0 - most_lost) * total, f"only {kept} of {total} positions are free of close calls"
+    return a, b

@@ -101,8 +101,12 @@ def latent_attention(w: Dict[str, torch.Tensor], p: str, m: dict, h: torch.Tenso
     return out @ w[p + "o"].T
 
 
-def gated_recurrence(w: Dict[str, torch.Tensor], p: str, m: dict, h: torch.Tensor, eps: float) -> torch.Tensor:
-    """One state matrix [d, e] per head; the forget gate f also sets how much is written (1 - f)."""
+def gated_recurrence(w: Dict[str, torch.Tensor], p: str, m: dict, h: torch.Tensor, eps: float,
+                     margins: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One state matrix [d, e] per head; the forget gate f also sets how much is written (1 - f).
+    ``margins`` [T]: the first token's output is v times the ONE number sum_d (1 - f_d) q_d, whose
+    sign alone survives the norm; position 0 takes that number's size relative to the sum of its
+    terms' sizes (the least over heads) if that is smaller than what is there."""
     T = h.shape[0]
     H, d, e = m["heads"], m["dim"], m["vdim"]
     q = silu(h @ w[p + "q"].T).view(T, H, d)
@@ -114,6 +118,10 @@ def gated_recurrence(w: Dict[str, torch.Tensor], p: str, m: dict, h: torch.Tenso
     for t in range(T):
         state = f[t][:, :, None] * state + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
         out[t] = torch.einsum("hde,hd->he", state, q[t])
+    if margins is not None:
+        terms = (1.0 - f[0]) * q[0]
+        rel = (terms.sum(dim=-1).abs() / terms.abs().sum(dim=-1).clamp_min(1e-300)).min()
+        margins[0] = torch.minimum(margins[0], rel.to(margins.dtype))
     out = unit_rms(out, eps) * w[p + "norm"]
     return out.reshape(T, H * e) @ w[p + "o"].T
 
@@ -137,10 +145,17 @@ def gated_attention(w: Dict[str, torch.Tensor], p: str, m: dict, h: torch.Tensor
     return out @ w[p + "o"].T
 
 
-def routed_experts(w: Dict[str, torch.Tensor], p: str, mlp: dict, x: torch.Tensor) -> torch.Tensor:
+def routed_experts(w: Dict[str, torch.Tensor], p: str, mlp: dict, x: torch.Tensor,
+                   margins: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``margins`` [T]: takes, where smaller, the gap between the last chosen logit and the best one
+    left out, relative to the largest |logit| of the token (how close the choice was)."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     logits = x @ w[p + "router"].T
     best, chosen = torch.topk(logits, top, dim=-1)
+    if margins is not None and top < E:
+        ordered = torch.sort(logits, dim=-1, descending=True).values
+        gap = (ordered[:, top - 1] - ordered[:, top]) / logits.abs().max(dim=-1).values.clamp_min(1e-300)
+        margins.copy_(torch.minimum(margins, gap.to(margins.dtype)))
     share = torch.softmax(best, dim=-1)
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
@@ -160,7 +175,10 @@ def token_input(w: Dict[str, torch.Tensor], p: str, x: torch.Tensor, ids: torch.
 
 
 def forward(config: dict, weights: Dict[str, torch.Tensor], token_ids: List[int], dtype=torch.float64,
-            layers_out: Optional[list] = None) -> torch.Tensor:
+            layers_out: Optional[list] = None, margins: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``margins`` (float64 [T], filled with inf by the caller) takes per position the closest of the
+    design's two kinds of close call (see ``routed_experts`` and ``gated_recurrence``): where it is small,
+    an implementation that rounds differently may rightly decide the other way."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     ids = torch.tensor(token_ids, dtype=torch.long)
@@ -177,14 +195,14 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], token_ids: List[int]
                 kept[i] = latent_cache(w, p + "mix.", m, h, positions, eps)
             y = latent_attention(w, p + "mix.", m, h, positions, eps, kept[m["kv_from"] if m.get("kv_from") is not None else i])
         elif layer["type"] == "hgrn2":
-            y = gated_recurrence(w, p + "mix.", m, h, eps)
+            y = gated_recurrence(w, p + "mix.", m, h, eps, margins)
         elif layer["type"] == "attention":
             y = gated_attention(w, p + "mix.", m, h, eps)
         else:
             raise ValueError(f"layer {i}: unknown type {layer['type']!r}")
         x = x + layer_norm(y, w[p + "norm1"], w[p + "norm1.b"], eps)
         if layer.get("mlp") is not None:
-            y = routed_experts(w, p + "mlp.", layer["mlp"], x)
+            y = routed_experts(w, p + "mlp.", layer["mlp"], x, margins)
             x = x + layer_norm(y, w[p + "norm2"], w[p + "norm2.b"], eps)
         if side:
             x = x + token_input(w, p + "side.", x, ids, w["side.embed"], i, side, eps)
