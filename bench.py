@@ -15,8 +15,8 @@ its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
 filled by real prefill steps for the end-to-end run and with random values for
 the device-timed runs (the work of a decode step does not depend on the values).
 
-``--design gitipel`` (or ``fokurax``) prints, instead of the record, prefill and decode of
-that design beside Qwen3 at equal layer sizes, with the time of every kernel.
+``--design gitipel`` (or ``fokurax``, ``pitudra``) prints, instead of the record, prefill and decode
+of that design beside Qwen3 (Pitudra: beside Fokurax) at equal layer sizes, with the time of every kernel.
 
 ``--timeline`` prints, instead of the record, when the CTAs of every kernel of one
 decode step started, waited and ended.  ``--shape`` runs the same at the Qwen3-0.6B or
@@ -417,6 +417,31 @@ def fokurax_config(width, heads, kv_heads, dim, ff, vocab=32768):
                        layer(experts, 4)]}
 
 
+def pitudra_config(width, heads, kv_heads, dim, ff, vocab=32768):
+    """Six layers, each with eight experts of half the dense size, two a token (as Fokurax's expert
+    layers; an expert here has two matrices, not three): a gated recurrence (heads of 64 key and
+    128 value channels over the whole width), latent attention (a latent of 192 numbers and a
+    rotated part of 64, 96 and 32 with heads of 64; queries through a latent of half the width),
+    plain attention with a sink and an output gate, latent attention on the second layer's cache,
+    and the first and third kind once more.  Windows of 1,024 positions, a token input of 256
+    features per layer."""
+    rot = dim // 2
+    experts = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
+
+    def latent(kv_from=None):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "q_rank": width // 2, "kv_rank": 3 * rot,
+             "rot": {"base": 1e6, "dims": rot}, "scale": (dim + rot) ** -0.5, "mask": {"size": 1024}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "latent_attention", "mixer": m, "mlp": experts}
+
+    recurrent = {"type": "hgrn2", "mixer": {"heads": width // 128, "dim": 64, "vdim": 128}, "mlp": experts}
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                                                "scale": dim ** -0.5, "mask": {"size": 1024}}, "mlp": experts}
+    return {"architecture": "Pitudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "token_side": {"dim": 256},
+            "layers": [recurrent, latent(), attention, latent(1), recurrent, attention]}
+
+
 def qwen3_config_like(width, heads, kv_heads, dim, ff, layers=6, vocab=32768):
     cfg = dict(QWEN3_8B)
     cfg.update(num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
@@ -484,9 +509,13 @@ def measure_design(name, cfg, vocab, prompt_tokens, batch, held, steps, warmup, 
 
 
 def compare_designs(sizes, prompt_tokens, batch, held, steps, warmup, design="gitipel"):
-    """Another design beside Qwen3 at equal layer sizes (six layer runs each, random weights)."""
-    make = {"gitipel": gitipel_config, "fokurax": fokurax_config}[design]
-    result = {"metric": f"prefill and decode of {design.capitalize()} beside Qwen3 at equal layer sizes", "layer_runs": 6,
+    """Another design beside Qwen3 at equal layer sizes (six layer runs each, random weights);
+    Pitudra beside Fokurax, the design nearest to it (routed experts, layers that read another
+    layer's cache, a token input per layer)."""
+    make = {"gitipel": gitipel_config, "fokurax": fokurax_config, "pitudra": pitudra_config}[design]
+    beside, make_other = ("fokurax", fokurax_config) if design == "pitudra" else ("qwen3", qwen3_config_like)
+    result = {"metric": f"prefill and decode of {design.capitalize()} beside {beside.capitalize()} at equal layer sizes",
+              "layer_runs": 6,
               "prompt_tokens": prompt_tokens, "decode_batch": batch, "decode_tokens_held": held, "dtype": "bf16",
               "data": "synthetic", "sizes": {}}
     for size in sizes:
@@ -494,8 +523,8 @@ def compare_designs(sizes, prompt_tokens, batch, held, steps, warmup, design="gi
         entry = {"width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "ff": ff}
         entry[design] = measure_design(design[0], make(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
                                        batch, held, steps, warmup)
-        entry["qwen3"] = measure_design("q", qwen3_config_like(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
-                                        batch, held, steps, warmup)
+        entry[beside] = measure_design("q", make_other(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
+                                       batch, held, steps, warmup)
         result["sizes"][size] = entry
     return result
 
@@ -577,9 +606,9 @@ def main() -> int:
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
                          "engine under two budgets and report how the runs agree")
-    ap.add_argument("--design", default=None, choices=["gitipel", "fokurax"],
-                    help="instead of the record: prefill and decode of this design beside Qwen3 at equal layer "
-                         "sizes (--design-sizes), with the time of every kernel")
+    ap.add_argument("--design", default=None, choices=["gitipel", "fokurax", "pitudra"],
+                    help="instead of the record: prefill and decode of this design beside Qwen3 (pitudra: beside "
+                         "fokurax) at equal layer sizes (--design-sizes), with the time of every kernel")
     ap.add_argument("--design-sizes", default="small,medium,large",
                     help="layer sizes for --design, with commas between them: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES),

@@ -282,11 +282,20 @@ __global__ void recurrence_gates_kernel(const TX* __restrict__ proj, long long s
     }
 }
 
-// grid (blocks of GR_COLS value columns, heads, sequences); 128 threads: eight neighbouring lanes share
-// a value column, each with R of the head's key rows of it in registers (row = i * 8 + part) from the
-// sequence's first token of the step to its last.  The tokens' q', f and v come through two buffers of
-// shared memory in chunks of GR_CHUNK tokens, the next chunk on its way (cp.async) while this one runs.
-constexpr int GR_COLS = 16, GR_PARTS = 8, GR_CHUNK = 16, GR_THREADS = GR_COLS * GR_PARTS;
+// grid (blocks of GR_COLS value columns, heads, sequences); one warp per value column, lane l with rows
+// l R .. l R + R - 1 of the head's key rows of that column in registers, from the sequence's first token
+// of the step to its last.  The tokens' q', f and v come through two buffers of shared memory in chunks
+// of GR_CHUNK tokens, the next chunk on its way (cp.async) while this one runs.  A token's row in a
+// buffer: q' of 32 R rows | f of 32 R rows | v of the block's columns; rows past d hold q' = 0 and
+// f = 1, tokens past the sequence's last q' = 0, f = 1 and v = 0, which leave state and sums as they are,
+// so the loop over a chunk's tokens has no condition in it.
+constexpr int GR_COLS = 16, GR_CHUNK = 16, GR_THREADS = GR_COLS * 32;
+
+__device__ __forceinline__ void gr_copy16(float* dst, const float* src)
+{
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(src) : "memory");
+}
 
 __device__ __forceinline__ void gr_copy4(float* dst, const float* src)
 {
@@ -295,79 +304,157 @@ __device__ __forceinline__ void gr_copy4(float* dst, const float* src)
 }
 
 template <int R>
+__device__ __forceinline__ void gr_load_rows(float (&dst)[R], const float* src)
+{
+    if constexpr (R % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(src + i);
+            dst[i] = x.x, dst[i + 1] = x.y, dst[i + 2] = x.z, dst[i + 3] = x.w;
+        }
+    } else if constexpr (R == 2) {
+        const float2 x = *reinterpret_cast<const float2*>(src);
+        dst[0] = x.x, dst[1] = x.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i)
+            dst[i] = src[i];
+    }
+}
+
+// Sums over the 32 lanes of N values per lane; lanes 2 k and 2 k + 1 end with value k's sum in a[0]
+// (N = 16).  Every exchange halves the values a lane still carries: N + 2 exchanges instead of 5 N.
+template <int N, int OFF>
+__device__ __forceinline__ void gr_fold(float (&a)[GR_CHUNK], bool upper)
+{
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) {
+        const float send = upper ? a[j] : a[j + N / 2];
+        const float keep = upper ? a[j + N / 2] : a[j];
+        a[j] = keep + __shfl_xor_sync(0xffffffffu, send, OFF);
+    }
+}
+
+template <int R>
 __global__ void __launch_bounds__(GR_THREADS)
 gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state, float* __restrict__ out,
                         const int* __restrict__ q_start, const int* __restrict__ state_slots, int heads, int d, int e)
 {
+    static_assert(GR_CHUNK == 16, "the fold below is written for 16 tokens");
     pdl_enter();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int head = blockIdx.y, seq = blockIdx.z;
     const int t0 = q_start[seq], t1 = q_start[seq + 1];
     if (t1 <= t0)
         return;
     const int tid = threadIdx.x;
-    const int col_in = tid / GR_PARTS, part = tid % GR_PARTS;
-    const int col = blockIdx.x * GR_COLS + col_in;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int col = blockIdx.x * GR_COLS + warp;
     const int kw = heads * d, vw = heads * e;
     const int width = 2 * kw + vw;
-    const int per_token = 2 * d + GR_COLS;                 // q' | f of the head, v of the block's columns
-    float* bufs[2] = {sm, sm + GR_CHUNK * per_token};
+    constexpr int ROWS = 32 * R;                            // d rounded up to the warp's rows
+    constexpr int PER_TOKEN = 2 * ROWS + GR_COLS;
     float S[R];
     float* st = state + (((long long)state_slots[seq] * heads + head) * d) * e;
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int r = i * GR_PARTS + part;
+        const int r = lane * R + i;
         S[i] = (r < d && col < e) ? st[(long long)r * e + col] : 0.f;
     }
+    // rows past d, in both buffers, once: no copy ever writes there
+    for (int i = tid; i < 2 * GR_CHUNK * (ROWS - d); i += GR_THREADS) {
+        const int tok = i / (ROWS - d), r = d + i % (ROWS - d);
+        sm[tok * PER_TOKEN + r] = 0.f;
+        sm[tok * PER_TOKEN + ROWS + r] = 1.f;
+    }
+    // 16 bytes a copy where every piece of a row starts on such a boundary, else 4
+    const bool wide = d % 4 == 0 && e % 4 == 0 && (reinterpret_cast<uintptr_t>(qfv) & 15) == 0;
     auto fetch = [&](int first, float* buf) {
         const int count = min(GR_CHUNK, t1 - first);
-        for (int i = tid; i < count * per_token; i += GR_THREADS) {
-            const int tok = i / per_token, w = i - tok * per_token;
-            const float* src = qfv + (long long)(first + tok) * width;
-            if (w < d)
-                src += head * d + w;
-            else if (w < 2 * d)
-                src += kw + head * d + (w - d);
-            else {
-                const int c = blockIdx.x * GR_COLS + (w - 2 * d);
-                src += 2 * kw + head * e + (c < e ? c : e - 1);
+        if (wide) {
+            const int dq = d / 4, units = 2 * dq + GR_COLS / 4;
+            for (int i = tid; i < count * units; i += GR_THREADS) {
+                const int tok = i / units, u = i - tok * units;
+                const float* src = qfv + (long long)(first + tok) * width;
+                float* dst = buf + tok * PER_TOKEN;
+                if (u < dq) {
+                    src += head * d + 4 * u;
+                    dst += 4 * u;
+                } else if (u < 2 * dq) {
+                    src += kw + head * d + 4 * (u - dq);
+                    dst += ROWS + 4 * (u - dq);
+                } else {
+                    const int c = blockIdx.x * GR_COLS + 4 * (u - 2 * dq);
+                    src += 2 * kw + head * e + (c < e ? c : e - 4);
+                    dst += 2 * ROWS + 4 * (u - 2 * dq);
+                }
+                gr_copy16(dst, src);
             }
-            gr_copy4(buf + i, src);
+        } else {
+            const int units = 2 * d + GR_COLS;
+            for (int i = tid; i < count * units; i += GR_THREADS) {
+                const int tok = i / units, w = i - tok * units;
+                const float* src = qfv + (long long)(first + tok) * width;
+                float* dst = buf + tok * PER_TOKEN;
+                if (w < d) {
+                    src += head * d + w;
+                    dst += w;
+                } else if (w < 2 * d) {
+                    src += kw + head * d + (w - d);
+                    dst += ROWS + (w - d);
+                } else {
+                    const int c = blockIdx.x * GR_COLS + (w - 2 * d);
+                    src += 2 * kw + head * e + (c < e ? c : e - 1);
+                    dst += 2 * ROWS + (w - 2 * d);
+                }
+                gr_copy4(dst, src);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        // the sequence ends inside this chunk: tokens that do nothing behind its last one
+        for (int i = tid; i < (GR_CHUNK - count) * PER_TOKEN; i += GR_THREADS) {
+            const int w = i % PER_TOKEN;
+            buf[count * PER_TOKEN + i] = (w >= ROWS && w < 2 * ROWS) ? 1.f : 0.f;
+        }
     };
-    fetch(t0, bufs[0]);
+    fetch(t0, sm);
+    const bool writes = (lane & 1) == 0 && col < e;
     int which = 0;
     for (int first = t0; first < t1; first += GR_CHUNK, which ^= 1) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();            // this chunk has arrived, and everyone has left the other buffer
         if (first + GR_CHUNK < t1)
-            fetch(first + GR_CHUNK, bufs[which ^ 1]);
-        const float* buf = bufs[which];
-        const int count = min(GR_CHUNK, t1 - first);
-        for (int tok = 0; tok < count; ++tok) {
-            const float* q = buf + tok * per_token + part;
-            const float* f = q + d;
-            const float v = buf[tok * per_token + 2 * d + col_in];
+            fetch(first + GR_CHUNK, sm + (which ^ 1) * GR_CHUNK * PER_TOKEN);
+        const float* buf = sm + which * GR_CHUNK * PER_TOKEN;
+        // The state's chain is one multiply-add per element and token.  A token's sum over the key rows
+        // stays spread over the lanes until the chunk is through; the exchanges follow for all of them.
+        float accs[GR_CHUNK];
+#pragma unroll
+        for (int tok = 0; tok < GR_CHUNK; ++tok) {
+            float q[R], f[R];
+            gr_load_rows<R>(q, buf + tok * PER_TOKEN + lane * R);
+            gr_load_rows<R>(f, buf + tok * PER_TOKEN + ROWS + lane * R);
+            const float v = buf[tok * PER_TOKEN + 2 * ROWS + warp];
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                if (i * GR_PARTS + part < d) {
-                    const float fi = f[i * GR_PARTS];
-                    S[i] = fmaf(fi, S[i], (1.f - fi) * v);
-                    acc = fmaf(S[i], q[i * GR_PARTS], acc);
-                }
+                S[i] = fmaf(f[i], S[i], (1.f - f[i]) * v);
+                acc = fmaf(S[i], q[i], acc);
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (part == 0 && col < e)
-                out[(long long)(first + tok) * vw + head * e + col] = acc;
+            accs[tok] = acc;
         }
+        gr_fold<16, 16>(accs, lane & 16);
+        gr_fold<8, 8>(accs, lane & 8);
+        gr_fold<4, 4>(accs, lane & 4);
+        gr_fold<2, 2>(accs, lane & 2);
+        const float total = accs[0] + __shfl_xor_sync(0xffffffffu, accs[0], 1);
+        const int tok = lane >> 1;
+        if (writes && first + tok < t1)
+            out[(long long)(first + tok) * vw + head * e + col] = total;
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int r = i * GR_PARTS + part;
+        const int r = lane * R + i;
         if (r < d && col < e)
             st[(long long)r * e + col] = S[i];
     }
@@ -565,25 +652,25 @@ CHIBI_API int chibi_gated_recurrence(const float* qfv, float* state, float* out,
         return CHIBI_OK;
     if (!qfv || !state || !out || !q_start || !state_slots || heads <= 0 || d <= 0 || e <= 0)
         return CHIBI_ERR_ARGUMENT;
-    if (d > 32 * GR_PARTS || heads > 65535 || seqs > 65535)
+    if (d > 32 * 8 || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)((e + GR_COLS - 1) / GR_COLS), (unsigned)heads, (unsigned)seqs);
-    const size_t smem = (size_t)2 * GR_CHUNK * (2 * d + GR_COLS) * sizeof(float);
 #define CHIBI_GR_LAUNCH(R)                                                                                       \
     do {                                                                                                         \
         auto kernel = gated_recurrence_kernel<R>;                                                                \
+        const size_t smem = (size_t)2 * GR_CHUNK * (64 * R + GR_COLS) * sizeof(float);                           \
         if (smem > 48 * 1024)                                                                                    \
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
         launch(kernel, grid, dim3(GR_THREADS), smem, stream, qfv, state, out, q_start, state_slots, heads, d, e); \
     } while (0)
-    if (d <= 4 * GR_PARTS)
+    if (d <= 32)
+        CHIBI_GR_LAUNCH(1);
+    else if (d <= 64)
+        CHIBI_GR_LAUNCH(2);
+    else if (d <= 128)
         CHIBI_GR_LAUNCH(4);
-    else if (d <= 8 * GR_PARTS)
-        CHIBI_GR_LAUNCH(8);
-    else if (d <= 16 * GR_PARTS)
-        CHIBI_GR_LAUNCH(16);
     else
-        CHIBI_GR_LAUNCH(32);
+        CHIBI_GR_LAUNCH(8);
 #undef CHIBI_GR_LAUNCH
     return launch_status();
 }
