@@ -54,6 +54,41 @@ __global__ void rmsnorm_kernel(const TX* x, const TW* __restrict__ w, TO* out,  
     }
 }
 
+// Many short 32-bit rows with 32-bit weights (a norm per head: n is a head's width): a warp to a row,
+// eight rows a block, so that a row costs no block of its own and no barrier.
+constexpr int SHORT_ROW_WARPS = 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(SHORT_ROW_WARPS * 32)
+rmsnorm_short_rows_kernel(const float* x, const float* __restrict__ w, TO* out, long long groups, int n,
+                          long long x_stride, long long out_stride, float eps, float offset)
+{
+    pdl_enter();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool wide = n % 4 == 0 && x_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    for (long long g = (long long)blockIdx.x * SHORT_ROW_WARPS + warp; g < groups;
+         g += (long long)gridDim.x * SHORT_ROW_WARPS) {
+        const float* row = x + g * x_stride;
+        TO* dst = out + g * out_stride;
+        float s = 0.f;
+        if (wide) {
+            for (int j = 4 * lane; j < n; j += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(row + j);
+                s = fmaf(v.x, v.x, s), s = fmaf(v.y, v.y, s), s = fmaf(v.z, v.z, s), s = fmaf(v.w, v.w, s);
+            }
+        } else {
+            for (int j = lane; j < n; j += 32)
+                s = fmaf(row[j], row[j], s);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1)
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float inv = rsqrtf(s / (float)n + eps);
+        for (int j = lane; j < n; j += 32)
+            dst[j] = from_f32<TO>((row[j] * inv) * (w[j] + offset));
+    }
+}
+
 // The same for 32-bit rows and bfloat16 weights and output, n a multiple of 4
 // and at most 16 * blockDim.x: the row stays in registers between the two passes.
 __global__ void __launch_bounds__(512)
@@ -672,6 +707,15 @@ CHIBI_API int chibi_rmsnorm(const void* x, int x_type, const void* w, int w_type
     int block = 32;
     while (block < n && block < 512)
         block <<= 1;
+    if (x_type == CHIBI_F32 && w_type == CHIBI_F32 && n <= 1024 && x != out) {
+        const long long blocks = (groups + SHORT_ROW_WARPS - 1) / SHORT_ROW_WARPS;
+        const dim3 grid((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8));
+        CHIBI_DISPATCH_TYPE(out_type, TO, {
+            launch(rmsnorm_short_rows_kernel<TO>, grid, dim3(SHORT_ROW_WARPS * 32), 0, stream, (const float*)x,
+                   (const float*)w, (TO*)out, groups, n, x_stride, out_stride, eps, offset);
+        });
+        return launch_status();
+    }
     if (x_type == CHIBI_F32 && w_type == CHIBI_BF16 && out_type == CHIBI_BF16 && n % 4 == 0
         && n <= 16 * 512 && x_stride % 4 == 0 && out_stride % 4 == 0
         && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0

@@ -105,7 +105,7 @@ token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mix, f
 // ---------------------------------------------------------------- latents
 // One block per token.  Row: q_rank | kv_rank | rot columns (the last two only with a cache).
 template <typename TX, typename TC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_prepare_kernel(const TX* __restrict__ proj, long long stride, TX* __restrict__ cq, TC* __restrict__ k_cache,
                       const float* __restrict__ q_norm, const float* __restrict__ kv_norm, float eps,
                       const float* __restrict__ inv_freq, int q_rank, int kv_rank, int rot,
@@ -239,46 +239,89 @@ qkv_bias_norm_append_kernel(const TX* __restrict__ proj, long long stride, TX* _
     }
 }
 
-template <typename TX>
-__global__ void sigmoid_gate_kernel(TX* __restrict__ x, const TX* __restrict__ gate, long long gate_stride,
-                                    long long rows, int n)
+// Four neighbouring columns of a row at once (V = 4) where the rows allow it, else one; grid (column
+// blocks, rows): no division per element.
+template <typename T, int V>
+__device__ __forceinline__ void load_columns(float (&dst)[V], const T* src)
+{
+    if constexpr (V == 4 && sizeof(T) == 4) {
+        const float4 x = *reinterpret_cast<const float4*>(src);
+        dst[0] = x.x, dst[1] = x.y, dst[2] = x.z, dst[3] = x.w;
+    } else if constexpr (V == 4) {
+        const uint2 x = *reinterpret_cast<const uint2*>(src);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+        dst[0] = __low2float(lo), dst[1] = __high2float(lo), dst[2] = __low2float(hi), dst[3] = __high2float(hi);
+    } else {
+        dst[0] = to_f32(src[0]);
+    }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void store_columns(T* dst, const float (&src)[V])
+{
+    if constexpr (V == 4 && sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(src[0], src[1], src[2], src[3]);
+    } else if constexpr (V == 4) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(src[0], src[1]), hi = __floats2bfloat162_rn(src[2], src[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<const uint32_t*>(&lo), x.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst) = x;
+    } else {
+        dst[0] = from_f32<T>(src[0]);
+    }
+}
+
+template <typename TX, int V>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(TX* __restrict__ x, const TX* __restrict__ gate, long long gate_stride, long long rows, int n)
 {
     pdl_enter();
-    const long long total = rows * n;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const long long t = i / n;
-        const int c = (int)(i - t * n);
-        const float g = to_f32(gate[t * gate_stride + c]);
-        x[i] = from_f32<TX>(to_f32(x[i]) / (1.f + expf(-g)));
+    const int c = (blockIdx.x * 256 + threadIdx.x) * V;
+    if (c >= n)
+        return;
+    for (long long t = blockIdx.y; t < rows; t += gridDim.y) {
+        float a[V], g[V];
+        load_columns<TX, V>(a, x + t * n + c);
+        load_columns<TX, V>(g, gate + t * gate_stride + c);
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            a[i] = a[i] / (1.f + expf(-g[i]));
+        store_columns<TX, V>(x + t * n + c, a);
     }
 }
 
 // ---------------------------------------------------------------- gated linear recurrence
 // out [T, 2 kw + vw] 32-bit: silu(q) | l + (1 - l) sigmoid(f + b) | v, from a row q | f | v.
-template <typename TX>
-__global__ void recurrence_gates_kernel(const TX* __restrict__ proj, long long stride, const float* __restrict__ bias,
-                                        const float* __restrict__ floor_, float* __restrict__ out, long long rows,
-                                        int kw, int vw)
+template <typename TX, int V>
+__global__ void __launch_bounds__(256)
+recurrence_gates_kernel(const TX* __restrict__ proj, long long stride, const float* __restrict__ bias,
+                        const float* __restrict__ floor_, float* __restrict__ out, long long rows, int kw, int vw)
 {
     pdl_enter();
     const int w = 2 * kw + vw;
-    const long long total = rows * w;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const long long t = i / w;
-        const int c = (int)(i - t * w);
-        const float v = to_f32(proj[t * stride + c]);
-        float r;
+    const int c = (blockIdx.x * 256 + threadIdx.x) * V;        // with V = 4, kw and vw are multiples of 4
+    if (c >= w)
+        return;
+    float l[V], b[V];
+    if (c >= kw && c < 2 * kw) {
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            l[i] = floor_[c - kw + i], b[i] = bias[c - kw + i];
+    }
+    for (long long t = blockIdx.y; t < rows; t += gridDim.y) {
+        float v[V];
+        load_columns<TX, V>(v, proj + t * stride + c);
         if (c < kw) {
-            r = v / (1.f + expf(-v));
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                v[i] = v[i] / (1.f + expf(-v[i]));
         } else if (c < 2 * kw) {
-            const float l = floor_[c - kw];
-            r = l + (1.f - l) / (1.f + expf(-(v + bias[c - kw])));
-        } else {
-            r = v;
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                v[i] = l[i] + (1.f - l[i]) / (1.f + expf(-(v[i] + b[i])));
         }
-        out[i] = r;
+        store_columns<float, V>(out + t * w + c, v);
     }
 }
 
@@ -289,7 +332,7 @@ __global__ void recurrence_gates_kernel(const TX* __restrict__ proj, long long s
 // buffer: q' of 32 R rows | f of 32 R rows | v of the block's columns; rows past d hold q' = 0 and
 // f = 1, tokens past the sequence's last q' = 0, f = 1 and v = 0, which leave state and sums as they are,
 // so the loop over a chunk's tokens has no condition in it.
-constexpr int GR_COLS = 16, GR_CHUNK = 16, GR_THREADS = GR_COLS * 32;
+constexpr int GR_COLS = 16, GR_CHUNK = 16, GR_THREADS = GR_COLS * 32, GR_PITCH = GR_COLS + 1;
 
 __device__ __forceinline__ void gr_copy16(float* dst, const float* src)
 {
@@ -356,10 +399,13 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
     constexpr int PER_TOKEN = 2 * ROWS + GR_COLS;
     float S[R];
     float* st = state + (((long long)state_slots[seq] * heads + head) * d) * e;
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int r = lane * R + i;
-        S[i] = (r < d && col < e) ? st[(long long)r * e + col] : 0.f;
+    // The block's piece of the state, d rows of GR_COLS columns, comes and goes through shared memory:
+    // sixteen neighbouring threads take a row's 64 bytes, where a lane's own rows lie a whole row apart.
+    float* tile = sm + 2 * GR_CHUNK * PER_TOKEN;
+    for (int i = tid; i < d * GR_COLS; i += GR_THREADS) {
+        const int r = i / GR_COLS, c = i % GR_COLS;
+        const int cc = blockIdx.x * GR_COLS + c;
+        tile[r * GR_PITCH + c] = cc < e ? st[(long long)r * e + cc] : 0.f;
     }
     // rows past d, in both buffers, once: no copy ever writes there
     for (int i = tid; i < 2 * GR_CHUNK * (ROWS - d); i += GR_THREADS) {
@@ -418,6 +464,12 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
         }
     };
     fetch(t0, sm);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int r = lane * R + i;
+        S[i] = r < d ? tile[r * GR_PITCH + warp] : 0.f;
+    }
     const bool writes = (lane & 1) == 0 && col < e;
     int which = 0;
     for (int first = t0; first < t1; first += GR_CHUNK, which ^= 1) {
@@ -455,8 +507,15 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int r = lane * R + i;
-        if (r < d && col < e)
-            st[(long long)r * e + col] = S[i];
+        if (r < d)
+            tile[r * GR_PITCH + warp] = S[i];       // everyone took its rows from here before the first chunk
+    }
+    __syncthreads();
+    for (int i = tid; i < d * GR_COLS; i += GR_THREADS) {
+        const int r = i / GR_COLS, c = i % GR_COLS;
+        const int cc = blockIdx.x * GR_COLS + c;
+        if (cc < e)
+            st[(long long)r * e + cc] = tile[r * GR_PITCH + c];
     }
 }
 
@@ -517,13 +576,6 @@ router_top_kernel(const float* __restrict__ logits, long long stride, int* __res
     }
 }
 
-static inline unsigned grid_for(long long total, int threads)
-{
-    long long b = (total + threads - 1) / threads;
-    if (b < 1)
-        b = 1;
-    return (unsigned)(b > 148LL * 16 ? 148LL * 16 : b);
-}
 
 } // namespace chibi
 
@@ -580,7 +632,7 @@ CHIBI_API int chibi_latent_prepare(const void* proj, int x_type, long long strid
                     || rot % 2 || page_size <= 0))
         return CHIBI_ERR_ARGUMENT;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(cache_type, TC, {
-        launch(latent_prepare_kernel<TX, TC>, dim3((unsigned)rows), dim3(128), 0, stream, (const TX*)proj, stride,
+        launch(latent_prepare_kernel<TX, TC>, dim3((unsigned)rows), dim3(256), 0, stream, (const TX*)proj, stride,
                (TX*)cq, (TC*)k_cache, q_norm, kv_norm, eps, inv_freq, q_rank, kv_rank, rot, positions, seq_of_token,
                seq_rows, block_table, table_stride, page_size, num_pages, error);
     }));
@@ -623,9 +675,17 @@ CHIBI_API int chibi_sigmoid_gate(void* x, const void* gate, int x_type, long lon
         return CHIBI_OK;
     if (!x || !gate)
         return CHIBI_ERR_ARGUMENT;
+    const size_t unit = x_type == CHIBI_F32 ? 16 : 8;       // bytes of four columns
+    const bool wide = n % 4 == 0 && gate_stride % 4 == 0 && reinterpret_cast<uintptr_t>(x) % unit == 0
+                      && reinterpret_cast<uintptr_t>(gate) % unit == 0;
+    const unsigned row_blocks = (unsigned)(rows < 16384 ? rows : 16384);
     CHIBI_DISPATCH_TYPE(x_type, TX, {
-        launch(sigmoid_gate_kernel<TX>, dim3(grid_for(rows * n, 256)), dim3(256), 0, stream, (TX*)x, (const TX*)gate,
-               gate_stride, rows, n);
+        if (wide)
+            launch(sigmoid_gate_kernel<TX, 4>, dim3((unsigned)((n / 4 + 255) / 256), row_blocks), dim3(256), 0, stream,
+                   (TX*)x, (const TX*)gate, gate_stride, rows, n);
+        else
+            launch(sigmoid_gate_kernel<TX, 1>, dim3((unsigned)((n + 255) / 256), row_blocks), dim3(256), 0, stream,
+                   (TX*)x, (const TX*)gate, gate_stride, rows, n);
     });
     return launch_status();
 }
@@ -638,9 +698,18 @@ CHIBI_API int chibi_recurrence_gates(const void* proj, int x_type, long long str
         return CHIBI_OK;
     if (!proj || !bias || !floor_ || !out || kw <= 0 || vw <= 0)
         return CHIBI_ERR_ARGUMENT;
+    const int w = 2 * kw + vw;
+    const size_t unit = x_type == CHIBI_F32 ? 16 : 8;
+    const bool wide = kw % 4 == 0 && vw % 4 == 0 && stride % 4 == 0 && reinterpret_cast<uintptr_t>(proj) % unit == 0
+                      && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const unsigned row_blocks = (unsigned)(rows < 16384 ? rows : 16384);
     CHIBI_DISPATCH_TYPE(x_type, TX, {
-        launch(recurrence_gates_kernel<TX>, dim3(grid_for(rows * (2LL * kw + vw), 256)), dim3(256), 0, stream,
-               (const TX*)proj, stride, bias, floor_, out, rows, kw, vw);
+        if (wide)
+            launch(recurrence_gates_kernel<TX, 4>, dim3((unsigned)((w / 4 + 255) / 256), row_blocks), dim3(256), 0,
+                   stream, (const TX*)proj, stride, bias, floor_, out, rows, kw, vw);
+        else
+            launch(recurrence_gates_kernel<TX, 1>, dim3((unsigned)((w + 255) / 256), row_blocks), dim3(256), 0, stream,
+                   (const TX*)proj, stride, bias, floor_, out, rows, kw, vw);
     });
     return launch_status();
 }
@@ -658,7 +727,7 @@ CHIBI_API int chibi_gated_recurrence(const float* qfv, float* state, float* out,
 #define CHIBI_GR_LAUNCH(R)                                                                                       \
     do {                                                                                                         \
         auto kernel = gated_recurrence_kernel<R>;                                                                \
-        const size_t smem = (size_t)2 * GR_CHUNK * (64 * R + GR_COLS) * sizeof(float);                           \
+        const size_t smem = ((size_t)2 * GR_CHUNK * (64 * R + GR_COLS) + (size_t)d * GR_PITCH) * sizeof(float);                           \
         if (smem > 48 * 1024)                                                                                    \
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
         launch(kernel, grid, dim3(GR_THREADS), smem, stream, qfv, state, out, q_start, state_slots, heads, d, e); \

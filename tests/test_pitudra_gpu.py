@@ -309,7 +309,7 @@ def recurrence_reference(proj, bias, floor, H, d, e):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,d,e", [(2, 24, 16), (1, 130, 8), (4, 32, 64), (3, 64, 128), (6, 48, 32)])
+@pytest.mark.parametrize("H,d,e", [(2, 24, 16), (1, 130, 8), (4, 32, 64), (3, 64, 128), (6, 48, 32), (2, 200, 20), (1, 7, 5)])
 def test_gated_recurrence(kernels, dtype, H, d, e):
     """A long sequence in portions of every kind beside a second sequence that is decoded token by
     token; slots that were used before (their state set to zero by hand, as the manager does) and
@@ -365,7 +365,7 @@ def test_gated_recurrence(kernels, dtype, H, d, e):
 @pytest.mark.parametrize("T,D,F,E,top", [(1, 64, 40, 5, 2), (9, 96, 24, 3, 3), (300, 80, 100, 7, 1), (700, 128, 64, 4, 2),
                                          (33, 72, 130, 12, 5), (3, 96, 32, 6, 2), (1000, 160, 96, 5, 3),
                                          (130, 256, 224, 3, 1), (70, 192, 128, 40, 6), (5, 256, 320, 9, 3),
-                                         (2048, 256, 192, 8, 2), (1, 128, 64, 4, 4), (64, 320, 96, 16, 3)])
+                                         (2048, 256, 192, 8, 2), (1, 128, 64, 4, 4), (64, 352, 96, 14, 3)])
 def test_router_and_experts(kernels, dtype, T, D, F, E, top):
     """The router's choice (largest logits first, softmax over the chosen ones) and
     down(relu(up x)^2) of the chosen experts: few tokens, many, sizes that end inside a tile,
