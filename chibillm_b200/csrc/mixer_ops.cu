@@ -330,8 +330,8 @@ recurrence_gates_kernel(const TX* __restrict__ proj, long long stride, const flo
 // of the step to its last.  The tokens' q', f and v come through two buffers of shared memory in chunks
 // of GR_CHUNK tokens, the next chunk on its way (cp.async) while this one runs.  A token's row in a
 // buffer: q' of 32 R rows | f of 32 R rows | v of the block's columns; rows past d hold q' = 0 and
-// f = 1, tokens past the sequence's last q' = 0, f = 1 and v = 0, which leave state and sums as they are,
-// so the loop over a chunk's tokens has no condition in it.
+// f = 1, which leave state and sums as they are, so the loop over a whole chunk's tokens has no condition
+// in it.  The tokens of a chunk that is not full go one by one.
 constexpr int GR_COLS = 16, GR_CHUNK = 16, GR_THREADS = GR_COLS * 32, GR_PITCH = GR_COLS + 1;
 
 __device__ __forceinline__ void gr_copy16(float* dst, const float* src)
@@ -457,11 +457,6 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        // the sequence ends inside this chunk: tokens that do nothing behind its last one
-        for (int i = tid; i < (GR_CHUNK - count) * PER_TOKEN; i += GR_THREADS) {
-            const int w = i % PER_TOKEN;
-            buf[count * PER_TOKEN + i] = (w >= ROWS && w < 2 * ROWS) ? 1.f : 0.f;
-        }
     };
     fetch(t0, sm);
     __syncthreads();
@@ -478,6 +473,28 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
         if (first + GR_CHUNK < t1)
             fetch(first + GR_CHUNK, sm + (which ^ 1) * GR_CHUNK * PER_TOKEN);
         const float* buf = sm + which * GR_CHUNK * PER_TOKEN;
+        const int count = min(GR_CHUNK, t1 - first);
+        if (count < GR_CHUNK) {
+            // the sequence's last tokens (a decode step's only one): one by one, each summed at once
+            for (int tok = 0; tok < count; ++tok) {
+                float q[R], f[R];
+                gr_load_rows<R>(q, buf + tok * PER_TOKEN + lane * R);
+                gr_load_rows<R>(f, buf + tok * PER_TOKEN + ROWS + lane * R);
+                const float v = buf[tok * PER_TOKEN + 2 * ROWS + warp];
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    S[i] = fmaf(f[i], S[i], (1.f - f[i]) * v);
+                    acc = fmaf(S[i], q[i], acc);
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1)
+                    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0 && col < e)
+                    out[(long long)(first + tok) * vw + head * e + col] = acc;
+            }
+            break;
+        }
         // The state's chain is one multiply-add per element and token.  A token's sum over the key rows
         // stays spread over the lanes until the chunk is through; the exchanges follow for all of them.
         float accs[GR_CHUNK];
@@ -501,7 +518,7 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
         gr_fold<2, 2>(accs, lane & 2);
         const float total = accs[0] + __shfl_xor_sync(0xffffffffu, accs[0], 1);
         const int tok = lane >> 1;
-        if (writes && first + tok < t1)
+        if (writes)
             out[(long long)(first + tok) * vw + head * e + col] = total;
     }
 #pragma unroll
