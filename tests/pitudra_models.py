@@ -80,6 +80,16 @@ CONFIGS: Dict[str, dict] = {
            "layers": [recurrent(1, 130, 8, mlp=moe(16, 3, 2)),
                       attention(1, 1, 40, vdim=8, window=1),
                       latent(1, 8, 16, 8, 8, 16, window=64, mlp=moe(16, 3, 2))]},
+    # odd sizes throughout: a cache row of 33 numbers, heads of 20 and 12, a recurrent head of 7 x 5; plain
+    # attention first; two recurrent layers in a row; two readers of one source; a window of exactly one
+    # page of 16 and one of a page and a position; a single expert
+    "P6": {"architecture": "Pitudra", "vocab": 131, "width": 72, "norm": {"eps": 1e-5}, "token_side": {"dim": 13},
+           "layers": [attention(6, 2, 20, vdim=12, window=16, mlp=moe(40, 6, 2)),
+                      latent(3, 10, 6, 14, 22, 27, window=17, base=777.0, mlp=moe(24, 1, 1)),
+                      recurrent(5, 7, 5, mlp=moe(8, 2, 2)),
+                      recurrent(2, 33, 18),
+                      latent(2, 6, 6, 9, 11, 27, window=16, base=777.0, kv_from=1, mlp=moe(40, 6, 5)),
+                      latent(4, 4, 6, 5, 30, 27, base=777.0, kv_from=1)]},
 }
 
 

@@ -492,6 +492,7 @@ CASES = {
     "P3": (16, [5, 129, 260, 400], [400, 31, 129, 64, 350, 3, 222]),
     "P4": (8, [3, 64, 129, 190], [150, 20, 65, 2, 180, 99, 40]),
     "P5": (16, [4, 66, 140, 300], [300, 20, 131, 64, 150, 2, 90]),
+    "P6": (16, [3, 65, 150, 290], [290, 16, 130, 64, 170, 2, 49]),
 }
 SEED = 21
 

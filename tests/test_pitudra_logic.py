@@ -203,7 +203,8 @@ def test_plain_logits_depend_on_the_window_only(kind):
 
 # ------------------------------------------------------------------ the engine on the stand-in kernels
 @pytest.mark.parametrize("name,page_size,lengths", [("P1", 4, [1, 30, 75]), ("P2", 16, [2, 40, 70]),
-                                                    ("P4", 8, [3, 23, 66]), ("P5", 16, [5, 70])])
+                                                    ("P4", 8, [3, 23, 66]), ("P5", 16, [5, 70]),
+                                                    ("P6", 16, [2, 35, 66])])
 def test_cutting_and_batching_on_cpu(tmp_path, name, page_size, lengths):
     cfg = pitudra_models.get(name)
     folder = pitudra_models.write_model(cfg, str(tmp_path / name), seed=11)
