@@ -145,7 +145,8 @@ def attention_reference(q, k, v, sink, scale, window):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,e,window", [
     (4, 2, 16, 16, 7), (3, 1, 48, 32, 40), (8, 1, 64, 64, 100), (2, 2, 128, 128, 33), (5, 1, 80, None, 130),
-    (2, 1, 40, None, 9), (1, 1, 24, 72, 1), (6, 3, 32, 32, None), (4, 1, 256, None, 150), (2, 1, 272, None, 64), (1, 1, 576, None, 200)])
+    (2, 1, 40, None, 9), (1, 1, 24, 72, 1), (6, 3, 32, 32, None), (4, 1, 256, None, 150), (2, 1, 272, None, 64), (1, 1, 576, None, 200),
+    (3, 1, 96, None, 50), (2, 2, 112, 112, 20), (2, 1, 160, None, 70), (2, 1, 208, None, 31)])
 def test_attention_with_a_window_and_a_sink(kernels, dtype, H, G, d, e, window):
     """Head sizes that the tensor-core kernels take (multiples of 16 up to 256 with values as wide
     as keys; 64 and 128: tcgen05 for prompt portions) and that they do not; values tied to the keys
