@@ -162,7 +162,7 @@ latent_prepare_kernel(const TX* __restrict__ proj, long long stride, TX* __restr
 // ---------------------------------------------------------------- q | k | v: biases, whole norm, append
 // One block per token; shared memory holds q | k with their biases in 32-bit.
 template <typename TX, typename TC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 qkv_bias_norm_append_kernel(const TX* __restrict__ proj, long long stride, TX* __restrict__ q_out,
                             TC* __restrict__ k_cache, TC* __restrict__ v_cache, const float* __restrict__ bias,
                             const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
@@ -325,14 +325,14 @@ recurrence_gates_kernel(const TX* __restrict__ proj, long long stride, const flo
     }
 }
 
-// grid (blocks of GR_COLS value columns, heads, sequences); one warp per value column, lane l with rows
+// grid (blocks of COLS value columns, heads, sequences); one warp per value column, lane l with rows
 // l R .. l R + R - 1 of the head's key rows of that column in registers, from the sequence's first token
 // of the step to its last.  The tokens' q', f and v come through two buffers of shared memory in chunks
 // of GR_CHUNK tokens, the next chunk on its way (cp.async) while this one runs.  A token's row in a
 // buffer: q' of 32 R rows | f of 32 R rows | v of the block's columns; rows past d hold q' = 0 and
 // f = 1, which leave state and sums as they are, so the loop over a whole chunk's tokens has no condition
 // in it.  The tokens of a chunk that is not full go one by one.
-constexpr int GR_COLS = 16, GR_CHUNK = 16, GR_THREADS = GR_COLS * 32, GR_PITCH = GR_COLS + 1;
+constexpr int GR_CHUNK = 16;
 
 __device__ __forceinline__ void gr_copy16(float* dst, const float* src)
 {
@@ -378,8 +378,8 @@ __device__ __forceinline__ void gr_fold(float (&a)[GR_CHUNK], bool upper)
     }
 }
 
-template <int R>
-__global__ void __launch_bounds__(GR_THREADS)
+template <int R, int COLS>
+__global__ void __launch_bounds__(COLS * 32)
 gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state, float* __restrict__ out,
                         const int* __restrict__ q_start, const int* __restrict__ state_slots, int heads, int d, int e)
 {
@@ -392,23 +392,24 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
         return;
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int col = blockIdx.x * GR_COLS + warp;
+    const int col = blockIdx.x * COLS + warp;
     const int kw = heads * d, vw = heads * e;
     const int width = 2 * kw + vw;
+    constexpr int THREADS = COLS * 32, PITCH = COLS + 1;
     constexpr int ROWS = 32 * R;                            // d rounded up to the warp's rows
-    constexpr int PER_TOKEN = 2 * ROWS + GR_COLS;
+    constexpr int PER_TOKEN = 2 * ROWS + COLS;
     float S[R];
     float* st = state + (((long long)state_slots[seq] * heads + head) * d) * e;
-    // The block's piece of the state, d rows of GR_COLS columns, comes and goes through shared memory:
+    // The block's piece of the state, d rows of COLS columns, comes and goes through shared memory:
     // sixteen neighbouring threads take a row's 64 bytes, where a lane's own rows lie a whole row apart.
     float* tile = sm + 2 * GR_CHUNK * PER_TOKEN;
-    for (int i = tid; i < d * GR_COLS; i += GR_THREADS) {
-        const int r = i / GR_COLS, c = i % GR_COLS;
-        const int cc = blockIdx.x * GR_COLS + c;
-        tile[r * GR_PITCH + c] = cc < e ? st[(long long)r * e + cc] : 0.f;
+    for (int i = tid; i < d * COLS; i += THREADS) {
+        const int r = i / COLS, c = i % COLS;
+        const int cc = blockIdx.x * COLS + c;
+        tile[r * PITCH + c] = cc < e ? st[(long long)r * e + cc] : 0.f;
     }
     // rows past d, in both buffers, once: no copy ever writes there
-    for (int i = tid; i < 2 * GR_CHUNK * (ROWS - d); i += GR_THREADS) {
+    for (int i = tid; i < 2 * GR_CHUNK * (ROWS - d); i += THREADS) {
         const int tok = i / (ROWS - d), r = d + i % (ROWS - d);
         sm[tok * PER_TOKEN + r] = 0.f;
         sm[tok * PER_TOKEN + ROWS + r] = 1.f;
@@ -418,8 +419,8 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
     auto fetch = [&](int first, float* buf) {
         const int count = min(GR_CHUNK, t1 - first);
         if (wide) {
-            const int dq = d / 4, units = 2 * dq + GR_COLS / 4;
-            for (int i = tid; i < count * units; i += GR_THREADS) {
+            const int dq = d / 4, units = 2 * dq + COLS / 4;
+            for (int i = tid; i < count * units; i += THREADS) {
                 const int tok = i / units, u = i - tok * units;
                 const float* src = qfv + (long long)(first + tok) * width;
                 float* dst = buf + tok * PER_TOKEN;
@@ -430,15 +431,15 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
                     src += kw + head * d + 4 * (u - dq);
                     dst += ROWS + 4 * (u - dq);
                 } else {
-                    const int c = blockIdx.x * GR_COLS + 4 * (u - 2 * dq);
+                    const int c = blockIdx.x * COLS + 4 * (u - 2 * dq);
                     src += 2 * kw + head * e + (c < e ? c : e - 4);
                     dst += 2 * ROWS + 4 * (u - 2 * dq);
                 }
                 gr_copy16(dst, src);
             }
         } else {
-            const int units = 2 * d + GR_COLS;
-            for (int i = tid; i < count * units; i += GR_THREADS) {
+            const int units = 2 * d + COLS;
+            for (int i = tid; i < count * units; i += THREADS) {
                 const int tok = i / units, w = i - tok * units;
                 const float* src = qfv + (long long)(first + tok) * width;
                 float* dst = buf + tok * PER_TOKEN;
@@ -449,7 +450,7 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
                     src += kw + head * d + (w - d);
                     dst += ROWS + (w - d);
                 } else {
-                    const int c = blockIdx.x * GR_COLS + (w - 2 * d);
+                    const int c = blockIdx.x * COLS + (w - 2 * d);
                     src += 2 * kw + head * e + (c < e ? c : e - 1);
                     dst += 2 * ROWS + (w - 2 * d);
                 }
@@ -463,7 +464,7 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int r = lane * R + i;
-        S[i] = r < d ? tile[r * GR_PITCH + warp] : 0.f;
+        S[i] = r < d ? tile[r * PITCH + warp] : 0.f;
     }
     const bool writes = (lane & 1) == 0 && col < e;
     int which = 0;
@@ -525,14 +526,14 @@ gated_recurrence_kernel(const float* __restrict__ qfv, float* __restrict__ state
     for (int i = 0; i < R; ++i) {
         const int r = lane * R + i;
         if (r < d)
-            tile[r * GR_PITCH + warp] = S[i];       // everyone took its rows from here before the first chunk
+            tile[r * PITCH + warp] = S[i];       // everyone took its rows from here before the first chunk
     }
     __syncthreads();
-    for (int i = tid; i < d * GR_COLS; i += GR_THREADS) {
-        const int r = i / GR_COLS, c = i % GR_COLS;
-        const int cc = blockIdx.x * GR_COLS + c;
+    for (int i = tid; i < d * COLS; i += THREADS) {
+        const int r = i / COLS, c = i % COLS;
+        const int cc = blockIdx.x * COLS + c;
         if (cc < e)
-            st[(long long)r * e + cc] = tile[r * GR_PITCH + c];
+            st[(long long)r * e + cc] = tile[r * PITCH + c];
     }
 }
 
@@ -678,7 +679,7 @@ CHIBI_API int chibi_qkv_bias_norm_append(const void* proj, int x_type, long long
         auto kernel = qkv_bias_norm_append_kernel<TX, TC>;
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch(kernel, dim3((unsigned)rows), dim3(256), smem, stream, (const TX*)proj, stride, (TX*)q_out,
+        launch(kernel, dim3((unsigned)rows), dim3(512), smem, stream, (const TX*)proj, stride, (TX*)q_out,
                (TC*)k_cache, (TC*)v_cache, bias, q_norm, k_norm, eps, inv_freq, rot, positions, seq_of_token, seq_rows,
                block_table, table_stride, nq, nkv, d, dv, page_size, num_pages, append, error);
     }));
@@ -740,14 +741,25 @@ CHIBI_API int chibi_gated_recurrence(const float* qfv, float* state, float* out,
         return CHIBI_ERR_ARGUMENT;
     if (d > 32 * 8 || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
-    const dim3 grid((unsigned)((e + GR_COLS - 1) / GR_COLS), (unsigned)heads, (unsigned)seqs);
-#define CHIBI_GR_LAUNCH(R)                                                                                       \
+    // 16 columns a block; 8 where that would leave SMs without a block (each column's arithmetic is the same
+    // either way)
+    const bool narrow = 2LL * ((e + 15) / 16) * heads * seqs <= 148;
+    const int cols = narrow ? 8 : 16;
+    const dim3 grid((unsigned)((e + cols - 1) / cols), (unsigned)heads, (unsigned)seqs);
+#define CHIBI_GR_LAUNCH_COLS(R, COLS)                                                                            \
     do {                                                                                                         \
-        auto kernel = gated_recurrence_kernel<R>;                                                                \
-        const size_t smem = ((size_t)2 * GR_CHUNK * (64 * R + GR_COLS) + (size_t)d * GR_PITCH) * sizeof(float);                           \
+        auto kernel = gated_recurrence_kernel<R, COLS>;                                                          \
+        const size_t smem = ((size_t)2 * GR_CHUNK * (64 * R + COLS) + (size_t)d * (COLS + 1)) * sizeof(float);   \
         if (smem > 48 * 1024)                                                                                    \
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
-        launch(kernel, grid, dim3(GR_THREADS), smem, stream, qfv, state, out, q_start, state_slots, heads, d, e); \
+        launch(kernel, grid, dim3(COLS * 32), smem, stream, qfv, state, out, q_start, state_slots, heads, d, e); \
+    } while (0)
+#define CHIBI_GR_LAUNCH(R)                                                                                       \
+    do {                                                                                                         \
+        if (narrow)                                                                                              \
+            CHIBI_GR_LAUNCH_COLS(R, 8);                                                                          \
+        else                                                                                                     \
+            CHIBI_GR_LAUNCH_COLS(R, 16);                                                                         \
     } while (0)
     if (d <= 32)
         CHIBI_GR_LAUNCH(1);
@@ -758,6 +770,7 @@ CHIBI_API int chibi_gated_recurrence(const float* qfv, float* state, float* out,
     else
         CHIBI_GR_LAUNCH(8);
 #undef CHIBI_GR_LAUNCH
+#undef CHIBI_GR_LAUNCH_COLS
     return launch_status();
 }
 
