@@ -42,12 +42,15 @@ class CachePlan:
     steps: Tuple[Optional[tuple], ...]
     tied: Tuple[str, ...] = ()      # groups whose values are their keys (no value arrays)
     value_dims: Tuple[Tuple[str, int], ...] = ()     # groups whose value heads have another size than their keys
+    value_heads: Tuple[Tuple[str, int], ...] = ()    # groups with fewer value heads than key heads
 
 
 def group_name(need: PagedKVNeed) -> str:
     base = f"kv{need.num_kv_heads}x{need.head_dim}" if not need.tied_values else f"k{need.num_kv_heads}x{need.head_dim}"
     if need.value_dim is not None and need.value_dim != need.head_dim:
         base += f"v{need.value_dim}"
+    if need.value_heads is not None and need.value_heads != need.num_kv_heads:
+        base += f"h{need.value_heads}"
     return base if need.window is None else f"{base}w{need.window}"
 
 
@@ -77,8 +80,10 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
                 raise CacheError("invalid_configuration",
                                  f"run step {i} reads the cache of step {src}, which owns no paged cache")
             theirs = needs_of[owner[1]]
-            if (need.num_kv_heads, need.head_dim, need.tied_values, need.value_dim or need.head_dim) != (
-                    theirs.num_kv_heads, theirs.head_dim, theirs.tied_values, theirs.value_dim or theirs.head_dim):
+            if (need.num_kv_heads, need.head_dim, need.tied_values, need.value_dim or need.head_dim,
+                    need.value_heads or need.num_kv_heads) != (
+                    theirs.num_kv_heads, theirs.head_dim, theirs.tied_values, theirs.value_dim or theirs.head_dim,
+                    theirs.value_heads or theirs.num_kv_heads):
                 raise CacheError("invalid_configuration",
                                  f"run step {i} cannot read the cache of step {src}: shapes differ")
             if need.window != theirs.window:
@@ -116,7 +121,9 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
                                entries[name], max_blocks) for name, n in needs_of.items())
     return CachePlan(groups, tuple(steps), tuple(name for name, n in needs_of.items() if n.tied_values),
                      tuple((name, n.value_dim) for name, n in needs_of.items()
-                           if n.value_dim is not None and n.value_dim != n.head_dim))
+                           if n.value_dim is not None and n.value_dim != n.head_dim),
+                     tuple((name, n.value_heads) for name, n in needs_of.items()
+                           if n.value_heads is not None and n.value_heads != n.num_kv_heads))
 
 
 class CacheStorage:
@@ -127,12 +134,14 @@ class CacheStorage:
         self.keys: Dict[str, torch.Tensor] = {}
         self.values: Dict[str, torch.Tensor] = {}
         value_dims = dict(plan.value_dims)
+        value_heads = dict(plan.value_heads)
         for g in plan.groups:
             shape = (g.num_entries, g.num_pages, g.num_kv_heads, g.page_size, g.head_dim)
             self.keys[g.name] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
             # a group whose values are its keys holds one array; readers get it under both names
             self.values[g.name] = self.keys[g.name] if g.name in plan.tied else \
-                torch.zeros(shape[:4] + (value_dims.get(g.name, g.head_dim),), dtype=runtime.dtype,
+                torch.zeros(shape[:2] + (value_heads.get(g.name, g.num_kv_heads), g.page_size,
+                                         value_dims.get(g.name, g.head_dim)), dtype=runtime.dtype,
                             device=runtime.device)
         # the block tables' mirror on the device: row = a request's state slot
         self.tables: Dict[str, torch.Tensor] = {

@@ -47,6 +47,11 @@ class PositionSpec:
     and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), frequency j becomes
     inv_freq[j] * (ramp_j / s + 1 - ramp_j), and cosines and sines are multiplied by
     ``amplitude_slope`` * ln(s) + 1.  0 switches it off.
+
+    ``wavelength_bands`` (factor, low, high, original), None = off: frequencies are divided by
+    ``factor`` according to their wavelength l = 2 pi / f.  l < original / high keeps f;
+    l > original / low gives f / factor; between the two, with
+    s = (original / l - low) / (high - low), the frequency is (1 - s) * f / factor + s * f.
     """
 
     kind: str
@@ -58,6 +63,7 @@ class PositionSpec:
     fast_turns: float = 0.0
     slow_turns: float = 0.0
     amplitude_slope: float = 0.0
+    wavelength_bands: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -97,6 +103,20 @@ class AttentionSpec(MixerSpec):
     multiplied by sigmoid(Wg x) (role "g_proj") before the output projection.
     ``cache_window``: how long the cache keeps a key where that is not ``window``
     (a layer whose cache a layer with a longer window reads); "same" = ``window``.
+
+    ``distance_bias`` "linear": slope[h] * (i - j) is taken off the score, with
+    slope[h] = 2 ** (-``distance_slope_bits`` * (h + 1) / num_heads); no tensors.
+    ``query_maps`` M > 1: every query head has M score maps (q has num_heads * M * head_dim
+    rows, k num_kv_heads * M * head_dim, a head's maps side by side), each an attention of its
+    own over the head's one value.  ``differential`` c (with two maps): the maps' outputs
+    a1, a2 are joined as o = a1 - lambda * a2 with
+    lambda = exp(sum(lq1 * lk1)) - exp(sum(lq2 * lk2)) + c (four vectors of head_dim numbers,
+    roles "lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2"), o is divided by its root mean
+    square over the head's values (``differential_eps`` inside the root, no weight) and
+    multiplied by 1 - c.  ``head_gate``: head h's output is multiplied by sigmoid(Wg x)[h], one
+    number per head (role "head_gate", [num_heads, hidden]), before the output projection.
+    ``biases`` together with ``qk_norm``: the biases are added first, then every q and k head is
+    normalised with the shared weight, then rotated.
     """
 
     hidden_size: int = 0
@@ -119,6 +139,50 @@ class AttentionSpec(MixerSpec):
     whole_norm_eps: Optional[float] = None
     output_gate: bool = False
     cache_window: object = "same"
+    distance_slope_bits: float = 8.0
+    query_maps: int = 1
+    differential: Optional[float] = None
+    differential_eps: float = 0.0
+    head_gate: bool = False
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec(MixerSpec):
+    """A selective state-space mixer with a scalar decay per head.  With inner =
+    ``num_heads`` * ``value_dim``, N = ``state_size`` and G = ``groups``, the input projection
+    (role "in_proj") gives z [inner] | x [inner] | B [G N] | C [G N] | dt [num_heads].  x | B | C
+    pass a causal convolution per channel (``conv_taps`` taps, role "conv" [channels, taps] with
+    the current token's tap last, bias role "conv_bias") and silu.  Per head h of group
+    floor(h / (num_heads / G)), with step = softplus(dt + dt_bias) (no clamp):
+
+        S <- exp(-exp(A_log[h]) * step) S + step * B x^T      (S is N by value_dim, 32-bit)
+        y  = S^T C + D[h] x
+
+    y * silu(z) is divided, in ``norm_groups`` equal parts, by each part's root mean square
+    (``norm_eps`` inside the root) and multiplied by a weight (role "out_norm"), then projected
+    (role "o_proj").  The state and the convolution's last ``conv_taps`` - 1 inputs are kept
+    per request (roles "dt_bias", "a_log", "skip" name the per-head vectors)."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    value_dim: int = 0
+    state_size: int = 0
+    groups: int = 1
+    conv_taps: int = 1
+    norm_groups: int = 1
+    norm_eps: float = 0.0
+
+
+@dataclass(frozen=True)
+class ParallelMixersSpec(MixerSpec):
+    """Two mixers side by side that read the same input; the result is
+    ``left_scale`` * left + ``right_scale`` * right.  The tensor roles of the two are those of
+    their kinds with "left." / "right." in front."""
+
+    left: MixerSpec = None
+    right: MixerSpec = None
+    left_scale: float = 1.0
+    right_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -222,12 +286,16 @@ class FeedForwardSpec:
 class GatedMLPSpec(FeedForwardSpec):
     """Dense gated feed-forward: down(act(gate(x)) * up(x)); ``activation`` "silu"
     or "gelu_tanh".  ``biases``: every one of the three products adds a vector
-    (tensor roles "gate_bias", "up_bias", "down_bias")."""
+    (tensor roles "gate_bias", "up_bias", "down_bias").  ``activation`` "swish_clamped":
+    g = min(gate(x), ``limit``), u = clamp(up(x), -``limit``, ``limit``) and the product is
+    down(g * sigmoid(``gate_slope`` * g) * (u + 1))."""
 
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
     biases: bool = False
+    limit: float = 0.0
+    gate_slope: float = 1.702
 
 
 @dataclass(frozen=True)
@@ -253,13 +321,32 @@ class RoutedExpertsSpec(FeedForwardSpec):
     (z = W_router x in 32-bit; role "router"), weighted by the softmax over the
     chosen logits only.  ``activation``: "relu2" (the square of relu), "relu",
     "silu", "gelu" or "gelu_tanh".  Tensor roles of expert e: "expert_up",
-    "expert_down", each a name with ``{e}`` where the number goes."""
+    "expert_down", each a name with ``{e}`` where the number goes.
+
+    ``gated``: an expert is down(act(gate(x)) * up(x)) (role "expert_gate" too).
+    ``scores`` "softmax_all": the router has ``num_experts`` + ``identity_experts`` outputs,
+    s = softmax over all of them, the choice goes by s + a correction per output (role
+    "correction", if ``correction``) and the weights are the chosen outputs' s (without the
+    correction) times ``weight_scale``, not renormalised.  ``group_count`` / ``group_keep``:
+    the outputs form ``group_count`` equal groups of neighbours, a group's score is its largest
+    choice score, and only outputs of the ``group_keep`` best groups can be chosen.  The last
+    ``identity_experts`` outputs name experts without tensors that return their input.
+    ``shared_size`` > 0: one more gated expert of that inner size (roles "shared_gate",
+    "shared_up", "shared_down") runs for every token with weight one."""
 
     hidden_size: int = 0
     intermediate_size: int = 0
     num_experts: int = 0
     top: int = 0
     activation: str = "relu2"
+    gated: bool = False
+    scores: str = "softmax_top"
+    correction: bool = False
+    group_count: int = 1
+    group_keep: int = 1
+    identity_experts: int = 0
+    weight_scale: float = 1.0
+    shared_size: int = 0
 
 
 @dataclass(frozen=True)
@@ -320,6 +407,9 @@ class LayerSpec:
     residual_scale: float = 1.0
     token_input: Optional[TokenInputSpec] = None
     token_shift: bool = False
+    # arrangement "prenorm": the mixer's and the feed-forward's results are multiplied feature by feature
+    # by a learned vector each (roles "mixer_scale", "feed_forward_scale") before they join the residual
+    layer_scale: bool = False
 
     def names(self) -> dict:
         return dict(self.weight_names)

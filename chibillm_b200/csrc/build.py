@@ -29,7 +29,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
 # name of library -> sources (relative to this folder)
 LIBRARIES: Dict[str, List[str]] = {
     "chibi_kernels": ["elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_generic.cu",
-                      "sampling.cu", "sequence_ops.cu", "layer_ops.cu", "experts_tcgen05.cu", "mixer_ops.cu"],
+                      "sampling.cu", "sequence_ops.cu", "layer_ops.cu", "experts_tcgen05.cu", "mixer_ops.cu", "hybrid_ops.cu"],
     # one library per head size: built with -DCHIBI_HEAD_DIM=<d> when a model needs it
     "chibi_attention_mma": ["attention_mma.cu"],
     # prompt attention on tcgen05, head sizes 64 and 128

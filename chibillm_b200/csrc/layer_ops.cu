@@ -182,7 +182,7 @@ __global__ void gated_activation_vec8_kernel(const __nv_bfloat16* __restrict__ g
 // table has a row per token of the step (a router's choices) instead of one per token id.
 __global__ void __launch_bounds__(1024)
 route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int vocab, int top, int experts,
-                      int num_tokens, int tile_rows, int max_tiles, int* __restrict__ offsets,
+                      int num_tokens, int tile_rows, int max_tiles, int with_weights, int* __restrict__ offsets,
                       int* __restrict__ pair_of_row, int* __restrict__ row_of_pair, int* __restrict__ tile_expert,
                       int* __restrict__ tile_row0, int* __restrict__ token_of_row, int* __restrict__ error)
 {
@@ -210,7 +210,8 @@ route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ ta
             offsets[e] = at;
             cursor[e] = at;
             const int end = at + counts[e];
-            for (int r = at; r < end && tile < max_tiles; r += tile_rows, ++tile) {
+            // (buckets from `with_weights` on get no tiles: their rows are filled by someone else)
+            for (int r = at; e < with_weights && r < end && tile < max_tiles; r += tile_rows, ++tile) {
                 tile_expert[tile] = e;
                 tile_row0[tile] = r;
             }
@@ -732,8 +733,22 @@ CHIBI_API int chibi_gated_activation(const void* gate_up, int x_type, long long 
 CHIBI_API int chibi_expert_tile_rows() { return EG_M; }
 CHIBI_API int chibi_expert_tile_rows_tensor_cores() { return TG_M; }
 
+CHIBI_API int chibi_route_by_table_open(const int* tokens, const int* table, int vocab, int top, int experts,
+                                        long long num_tokens, int tile_rows, int with_weights, int* route, int* error,
+                                        cudaStream_t stream);
+
 CHIBI_API int chibi_route_by_table(const int* tokens, const int* table, int vocab, int top, int experts,
                                    long long num_tokens, int tile_rows, int* route, int* error, cudaStream_t stream)
+{
+    return chibi_route_by_table_open(tokens, table, vocab, top, experts, num_tokens, tile_rows, experts, route, error,
+                                     stream);
+}
+
+// The same with buckets that have no matrices: the (token, choice) pairs of experts `with_weights` .. `experts` - 1
+// are sorted and counted like the others but get no tiles, so the products pass over them.
+CHIBI_API int chibi_route_by_table_open(const int* tokens, const int* table, int vocab, int top, int experts,
+                                        long long num_tokens, int tile_rows, int with_weights, int* route, int* error,
+                                        cudaStream_t stream)
 {
     if (num_tokens <= 0)
         return CHIBI_OK;
@@ -749,7 +764,8 @@ CHIBI_API int chibi_route_by_table(const int* tokens, const int* table, int voca
     int* tile_expert = row_of_pair + pairs;
     int* tile_row0 = tile_expert + max_tiles;
     launch(route_by_table_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), stream, tokens, table, vocab,
-           top, experts, (int)num_tokens, tile_rows, max_tiles, offsets, pair_of_row, row_of_pair, tile_expert, tile_row0,
+           top, experts, (int)num_tokens, tile_rows, max_tiles, with_weights, offsets, pair_of_row, row_of_pair,
+           tile_expert, tile_row0,
            tile_row0 + max_tiles, error);
     return launch_status();
 }

@@ -29,7 +29,8 @@ template <typename TX>
 __global__ void __launch_bounds__(128)
 short_conv_kernel(const TX* __restrict__ x, long long x_stride, const float* __restrict__ w, TX* history,
                   TX* __restrict__ out, long long out_stride, const int* __restrict__ q_start,
-                  const int* __restrict__ slots, int channels, int taps, int chunk)
+                  const int* __restrict__ slots, int channels, int taps, int chunk,
+                  const float* __restrict__ bias, int act, int add_input)
 {
     pdl_enter();
     const int ch = blockIdx.x * blockDim.x + threadIdx.x;
@@ -44,14 +45,16 @@ short_conv_kernel(const TX* __restrict__ x, long long x_stride, const float* __r
     TX* hist = history + (size_t)slots[seq] * (keep > 0 ? keep : 1) * channels;
     const float* wc = w + (size_t)ch * taps;
     for (int i = first; i < last; ++i) {
-        float y = to_f32(x[(size_t)(row0 + i) * x_stride + ch]);
+        float y = add_input ? to_f32(x[(size_t)(row0 + i) * x_stride + ch]) : 0.f;
+        if (bias)
+            y += bias[ch];
         for (int j = 0; j < taps; ++j) {
             const int m = i - keep + j;                    // token of the sequence's step, or before it
             const float v = m >= 0 ? to_f32(x[(size_t)(row0 + m) * x_stride + ch])
                                    : to_f32(hist[(size_t)(keep + m) * channels + ch]);
             y = fmaf(wc[j], v, y);
         }
-        out[(size_t)(row0 + i) * out_stride + ch] = from_f32<TX>(y);
+        out[(size_t)(row0 + i) * out_stride + ch] = from_f32<TX>(act >= 0 ? activate(y, act) : y);
     }
     if (first == 0) {
         // new history = the last `keep` entries of [old history ; this step's inputs], oldest first;
@@ -107,7 +110,8 @@ template <typename TX>
 __global__ void __launch_bounds__(128)
 short_conv_wide_kernel(const TX* __restrict__ x, long long x_stride, const float* __restrict__ wt, TX* history,
                        TX* __restrict__ out, long long out_stride, const int* __restrict__ q_start,
-                       const int* __restrict__ slots, int channels, int taps, int chunk)
+                       const int* __restrict__ slots, int channels, int taps, int chunk,
+                       const float* __restrict__ bias, int act, int add_input)
 {
     pdl_enter();
     constexpr int N = Pack<TX>::N;
@@ -123,7 +127,18 @@ short_conv_wide_kernel(const TX* __restrict__ x, long long x_stride, const float
     TX* hist = history + (size_t)slots[seq] * (keep > 0 ? keep : 1) * channels;
     for (int i = first; i < last; ++i) {
         float y[N];
-        Pack<TX>::load(x + (size_t)(row0 + i) * x_stride + ch, y);
+        if (add_input) {
+            Pack<TX>::load(x + (size_t)(row0 + i) * x_stride + ch, y);
+        } else {
+#pragma unroll
+            for (int e = 0; e < N; ++e)
+                y[e] = 0.f;
+        }
+        if (bias) {
+#pragma unroll
+            for (int e = 0; e < N; ++e)
+                y[e] += bias[ch + e];
+        }
         for (int j = 0; j < taps; ++j) {
             const int m = i - keep + j;
             float v[N], w[N];
@@ -134,6 +149,11 @@ short_conv_wide_kernel(const TX* __restrict__ x, long long x_stride, const float
 #pragma unroll
             for (int e = 0; e < N; ++e)
                 y[e] = fmaf(w[e], v[e], y[e]);
+        }
+        if (act >= 0) {
+#pragma unroll
+            for (int e = 0; e < N; ++e)
+                y[e] = activate(y[e], act);
         }
         Pack<TX>::store(out + (size_t)(row0 + i) * out_stride + ch, y);
     }
@@ -597,9 +617,12 @@ using namespace chibi;
 
 // `w`: [channels, taps]; `wt` (may be null): the same transposed, [taps, channels], for the kernel
 // that takes 16 bytes of channels per thread (taken when the sizes and addresses allow it).
-CHIBI_API int chibi_short_conv(const void* x, int x_type, long long x_stride, const float* w, const float* wt,
-                               void* history, void* out, long long out_stride, const int* q_start, const int* slots,
-                               int seqs, int max_q_len, int channels, int taps, cudaStream_t stream)
+// `bias` (may be null) is added to every sum, `act` (an activation's code, -1: none) applied to it; with
+// `add_input` the sum starts from the token's own input (y_t = x_t + ...), else from zero.
+CHIBI_API int chibi_causal_conv(const void* x, int x_type, long long x_stride, const float* w, const float* wt,
+                                void* history, void* out, long long out_stride, const int* q_start, const int* slots,
+                                int seqs, int max_q_len, int channels, int taps, const float* bias, int act,
+                                int add_input, cudaStream_t stream)
 {
     if (seqs <= 0 || max_q_len <= 0)
         return CHIBI_OK;
@@ -620,16 +643,24 @@ CHIBI_API int chibi_short_conv(const void* x, int x_type, long long x_stride, co
         const dim3 grid((unsigned)((threads + 127) / 128), (unsigned)chunks, (unsigned)seqs);
         CHIBI_DISPATCH_TYPE(x_type, TX, {
             launch(short_conv_wide_kernel<TX>, grid, dim3(128), 0, stream, (const TX*)x, x_stride, wt, (TX*)history,
-                   (TX*)out, out_stride, q_start, slots, channels, taps, chunk);
+                   (TX*)out, out_stride, q_start, slots, channels, taps, chunk, bias, act, add_input);
         });
         return launch_status();
     }
     const dim3 grid((unsigned)((channels + 127) / 128), (unsigned)chunks, (unsigned)seqs);
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         launch(short_conv_kernel<TX>, grid, dim3(128), 0, stream, (const TX*)x, x_stride, w, (TX*)history, (TX*)out,
-               out_stride, q_start, slots, channels, taps, chunk);
+               out_stride, q_start, slots, channels, taps, chunk, bias, act, add_input);
     });
     return launch_status();
+}
+
+CHIBI_API int chibi_short_conv(const void* x, int x_type, long long x_stride, const float* w, const float* wt,
+                               void* history, void* out, long long out_stride, const int* q_start, const int* slots,
+                               int seqs, int max_q_len, int channels, int taps, cudaStream_t stream)
+{
+    return chibi_causal_conv(x, x_type, x_stride, w, wt, history, out, out_stride, q_start, slots, seqs, max_q_len,
+                             channels, taps, nullptr, -1, 1, stream);
 }
 
 template <int R, int CPT, typename TX>

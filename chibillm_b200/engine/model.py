@@ -67,10 +67,13 @@ class DecoderModel:
 
     # ---- cache
     def cache_needs(self) -> List[object]:
-        return [self.blocks[step.layer].cache_need() for step in self.spec.run_order]
+        """One entry per run step, then one per input adapter that keeps something per request."""
+        return [self.blocks[step.layer].cache_need() for step in self.spec.run_order] \
+            + [a.cache_need() for a in self.input_adapters if a.cache_need() is not None]
 
     def cache_sources(self) -> List[Optional[int]]:
-        return [step.cache_of for step in self.spec.run_order]
+        return [step.cache_of for step in self.spec.run_order] \
+            + [None for a in self.input_adapters if a.cache_need() is not None]
 
     def launch_key(self, ctx: StepContext):
         """What the parts decide on the host from this batch's values (beyond its
@@ -100,8 +103,13 @@ class DecoderModel:
         hidden = self.spec.hidden_size
         residual = ctx.workspace.get("model.residual", (T, hidden), torch.float32)
         k.embed(ctx.tokens, self.embedding, residual)
+        view_at = len(self.spec.run_order)       # the adapters' views follow the run steps'
         for a in self.input_adapters:
-            a.forward(residual, ctx)
+            if a.cache_need() is not None:
+                a.forward(residual, ctx, cache=cache_views[view_at])
+                view_at += 1
+            else:
+                a.forward(residual, ctx)
         if self._keep_embedding_output:
             kept = ctx.workspace.get("model.embedding_output", (T, hidden), torch.float32)
             k.cast(residual, kept)

@@ -76,6 +76,21 @@ _SIGNATURES = {
         "chibi_expert_tile_rows": [],
         "chibi_expert_rows_tc": [P, P, P, L, P, L, I, I, I, I, I, P, P],
         "chibi_expert_tile_rows_tensor_cores": [],
+        "chibi_attention_generic_shared": [P, I, P, P, I, P, I, P, I, P, P, P, P, P, L, I, I, I, I, I, I, F, I, I, F, P, P,
+                                           P, I, P, P],
+        "chibi_causal_conv": [P, I, L, P, P, P, P, L, P, P, I, I, I, I, P, I, I, P],
+        "chibi_route_by_table_open": [P, P, I, I, I, L, I, I, P, P, P],
+        "chibi_bigram_embed": [P, P, I, P, P, P, P, P, P, L, I, I, L, L, P],
+        "chibi_stream_enter": [P, P, P, L, I, P],
+        "chibi_add_weighted": [P, P, F, P, F, L, P],
+        "chibi_heads_prepare_append": [P, I, L, P, P, P, F, P, I, P, P, P, P, L, P, P, P, I, L, I, I, I, I, I, I, I, P, P],
+        "chibi_differential_combine": [P, P, I, L, F, F, F, P, L, I, I, I, P],
+        "chibi_state_space_scan": [P, I, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "chibi_gated_group_rms": [P, P, I, L, P, F, P, L, I, I, P],
+        "chibi_clamped_swish_gate": [P, I, L, P, L, I, F, F, P],
+        "chibi_router_choose": [P, L, P, P, P, L, I, I, I, I, F, I, P],
+        "chibi_identity_rows": [P, I, L, P, P, L, I, I, I, I, P],
+        "chibi_scaled_add_norm": [P, P, P, P, I, F, F, P, I, L, I, P],
     },
     "chibi_attention_tc": {
         "chibi_attention_tc_head_dim": [],

@@ -756,7 +756,7 @@ class CudaKernels:
                   window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0,
                   seq_rows: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
                   distance_bias=None, chunk: Optional[int] = None, value_dim: Optional[int] = None,
-                  sink: Optional[torch.Tensor] = None) -> None:
+                  sink: Optional[torch.Tensor] = None, kv_share: int = 1) -> None:
         """Causal attention of every token over its sequence's pages.  bfloat16
         with a head size that is a multiple of 16 runs on the tensor cores (one
         library per head size, compiled when first needed); everything else, the
@@ -768,7 +768,10 @@ class CudaKernels:
         sequence's start.  ``value_dim``: the size of a value head where it is not d
         (the value cache is [pages, nkv, page, value_dim], out [T, nq * value_dim]);
         such a layer runs the plain kernel.  ``sink``, float32 [nq]: exp(sink[h]) joins the
-        softmax's denominator of head h (unscaled, once, with no value)."""
+        softmax's denominator of head h (unscaled, once, with no value).  ``distance_bias``
+        (slopes, None): slopes[h] * (i - j) is taken off instead.  ``kv_share`` n: n consecutive
+        key heads share one value head (the value cache has nkv / n heads).  ``out`` may be
+        float32 whatever q's type.  The last three run the plain kernel."""
         _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions,
                    seq_rows, sink)
         if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_contiguous()):
@@ -777,9 +780,11 @@ class CudaKernels:
         if distance_bias is not None:
             r1, r2 = distance_bias
             _need_cuda(r1, r2)
-            if r1.dtype != torch.float32 or r2.dtype != torch.float32 or r1.numel() != nq or r2.numel() != nq \
-                    or not r1.is_contiguous() or not r2.is_contiguous():
-                raise KernelError("attention: the distance bias is two contiguous float32 [nq] tensors")
+            for r in (r1, r2):
+                if r is not None and (r.dtype != torch.float32 or r.numel() != nq or not r.is_contiguous()):
+                    raise KernelError("attention: the distance bias is contiguous float32 [nq] tensors")
+            if r1 is None:
+                raise KernelError("attention: a distance bias needs its first tensor")
         cap = float(softcap) if softcap is not None else 0.0
         if cap < 0.0:
             raise KernelError("attention: the soft cap must be positive")
@@ -790,13 +795,26 @@ class CudaKernels:
             raise KernelError("attention: the chunk size must be positive")
         if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != (T, nq * dv):
             raise KernelError("attention: q must be contiguous [T, nq*d] and out [T, nq*value_dim]")
-        if out.dtype != q.dtype:
-            raise KernelError("attention: out must have q's element type")
+        if out.dtype != q.dtype and out.dtype != torch.float32:
+            raise KernelError("attention: out must have q's element type or be float32")
+        kv_share = int(kv_share)
+        if kv_share < 1 or nkv % kv_share != 0:
+            raise KernelError("attention: kv_share must divide the number of key heads")
         if (k_cache.dim() != 4 or v_cache.dim() != 4 or not k_cache.is_contiguous()
                 or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
-                or tuple(v_cache.shape) != (k_cache.shape[0], nkv, page_size, dv)):
+                or tuple(v_cache.shape) != (k_cache.shape[0], nkv // kv_share, page_size, dv)):
             raise KernelError(f"attention: cache shapes {tuple(k_cache.shape)} / {tuple(v_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
+        plain_only = kv_share != 1 or out.dtype != q.dtype or (r1 is not None and r2 is None)
+        if plain_only:
+            self.launches += 1
+            _check(self.lib.chibi_attention_generic_shared(
+                _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out), _code(out),
+                _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
+                _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, dv, page_size,
+                k_cache.shape[0], float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(sink),
+                kv_share, _ptr(self.error), self._stream()), "attention")
+            return
         if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
                 and d % 16 == 0 and d <= 256 and dv == d):
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
@@ -1487,19 +1505,27 @@ class CudaKernels:
 
     def chosen_experts(self, x: torch.Tensor, chosen: torch.Tensor, share: torch.Tensor, up: torch.Tensor,
                        down: torch.Tensor, acc: torch.Tensor, route: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
-                       kind: str, sorted_x: Optional[torch.Tensor] = None) -> None:
+                       kind: str, sorted_x: Optional[torch.Tensor] = None, gated: bool = False,
+                       interleaved: bool = False, identity: int = 0) -> None:
         """acc[t] += sum over s of share[t, s] * down_e (act(up_e x[t])), e = chosen[t, s]; up
         [E, F, D], down [E, D, F]; scratch as for ``routed_experts``.  The (token, choice)
         pairs are sorted by expert on the device and the two products run over tiles of one
-        expert's rows; nothing is read on the host."""
+        expert's rows; nothing is read on the host.  ``gated``: ``up`` is [E, 2 F, D], an
+        expert's gate rows followed by its up rows (``interleaved``: in blocks of 16, as
+        ``interleave_expert_gate_up`` lays them), and an expert is down(act(gate x) * (up x)).
+        ``identity`` n > 0: choice E - 1 names the experts that return their input (times the
+        share); the last of the E stacked matrices is a stand-in that is never read, and the
+        bucket of these choices gets no tiles: its rows take the tokens' inputs instead."""
         _need_cuda(x, chosen, share, up, down, acc, route, act, y)
         _rows_contiguous(x, "chosen_experts: x")
         _rows_contiguous(acc, "chosen_experts: acc")
         T, D = x.shape
         E, F, _ = up.shape
+        if gated:
+            F //= 2
         top = chosen.shape[1]
         pairs = T * top
-        if (up.shape != (E, F, D) or down.shape != (E, D, F) or not up.is_contiguous() or not down.is_contiguous()
+        if (up.shape != (E, (2 if gated else 1) * F, D) or down.shape != (E, D, F) or not up.is_contiguous() or not down.is_contiguous()
                 or down.dtype != up.dtype or chosen.dtype != torch.int32 or chosen.shape != (T, top)
                 or not chosen.is_contiguous() or share.shape != (T, top) or share.dtype != torch.float32
                 or not share.is_contiguous() or acc.dtype != torch.float32 or acc.shape != (T, D)
@@ -1512,11 +1538,21 @@ class CudaKernels:
         self.launches += 4
         # as ``routed_experts``: bfloat16 experts of sizes that are multiples of 32 run on the tensor cores
         # (tiles of 128 rows; multiples of 64: tcgen05), everything else the plain kernel
-        fast = up.dtype == torch.bfloat16 and self.expert_tensor_cores(x.dtype, D, F) and x.stride(0) % 8 == 0
+        fast = up.dtype == torch.bfloat16 and self.expert_tensor_cores(x.dtype, D, F) and x.stride(0) % 8 == 0 \
+            and (interleaved or not gated)
+        if gated and interleaved and not fast:
+            raise KernelError("chosen_experts: interleaved gate and up rows are for the tensor-core kernels")
         tile = self._expert_tile_rows[1 if fast else 0]
         code = self.ACTIVATIONS[kind]
-        _check(self.lib.chibi_route_by_table(None, _ptr(chosen), T, top, E, T, tile, _ptr(route), _ptr(self.error),
-                                             stream), "chosen_experts (route)")
+        first, rows_up, flag = (1, 2 * F, 1 if interleaved else 0) if gated else (2, F, 0)
+        if identity:
+            self.launches += 1          # (the choices come clamped to E - 1: ``router_choose``'s ``last_choice``)
+        _check(self.lib.chibi_route_by_table_open(None, _ptr(chosen), T, top, E, T, tile, E - 1 if identity else E,
+                                                  _ptr(route), _ptr(self.error), stream), "chosen_experts (route)")
+        if identity:
+            max_tiles = (pairs + tile - 1) // tile + E
+            _check(self.lib.chibi_identity_rows(_ptr(x), _code(x), x.stride(0), _ptr(route), _ptr(y), pairs, E, E - 1,
+                                                max_tiles, D, stream), "chosen_experts (identity rows)")
         if fast and sorted_x is not None and pairs >= self.EXPERTS_TCGEN05_MIN_PAIRS \
                 and self.experts_on_tcgen05(x.dtype, D, F):
             _need_cuda(sorted_x)
@@ -1526,8 +1562,8 @@ class CudaKernels:
             max_tiles = (pairs + tile - 1) // tile + E
             rows = route[E + 1 + 2 * pairs + 2 * max_tiles:E + 1 + 3 * pairs + 2 * max_tiles]
             self.gather_rows(x, rows, sorted_x)
-            s1 = self.lib.chibi_expert_rows_tc(_ptr(sorted_x), _ptr(up), _ptr(act), F, _ptr(route), pairs, E, F, D, 2,
-                                               code, _ptr(self.error), stream)
+            s1 = self.lib.chibi_expert_rows_tc(_ptr(sorted_x), _ptr(up), _ptr(act), F, _ptr(route), pairs, E, rows_up, D,
+                                               first, code, _ptr(self.error), stream)
             if s1 == 0:
                 _check(self.lib.chibi_expert_rows_tc(_ptr(act), _ptr(down), _ptr(y), D, _ptr(route), pairs, E, D, F, 0,
                                                      0, _ptr(self.error), stream), "chosen_experts (down, tcgen05)")
@@ -1538,7 +1574,7 @@ class CudaKernels:
             if s1 != -2:
                 _check(s1, "chosen_experts (up, tcgen05)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(x), _code(x), x.stride(0), 1, top, _ptr(up), _code(up), _ptr(act),
-                                               F, _ptr(route), pairs, E, F, D, 2, code, tile, 0, stream),
+                                               F, _ptr(route), pairs, E, F, D, first, code, tile, flag, stream),
                "chosen_experts (up)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(act), _code(act), F, 0, top, _ptr(down), _code(down), _ptr(y), D,
                                                _ptr(route), pairs, E, D, F, 0, 0, tile, 0, stream),
@@ -1612,6 +1648,233 @@ class CudaKernels:
                                         _code(table), table.stride(0), int(offset), table.shape[0], gate.shape[0],
                                         gate.shape[1], self.ACTIVATIONS[kind], _ptr(self.error), self._stream()),
                "side_gate")
+
+    # ---- parts of hybrid_ops.cu
+    def bigram_embed(self, residual: torch.Tensor, table: torch.Tensor, kept: torch.Tensor, tokens: torch.Tensor,
+                     positions: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor,
+                     state_slots: torch.Tensor, mul_prev: int, mul_cur: int) -> None:
+        """residual[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets], the last row of
+        the table ([buckets + 1, n]) for a sequence's first token.  The token before a step's first comes
+        from ``kept`` (int32 [slots, 1]), which then takes the sequence's last token of the step."""
+        _need_cuda(residual, table, kept, tokens, positions, seq_of_token, q_start, state_slots)
+        T, n = residual.shape
+        if residual.dtype != torch.float32 or not residual.is_contiguous() or table.dim() != 2 or table.shape[1] != n \
+                or table.shape[0] < 2 or not table.is_contiguous() or kept.dtype != torch.int32 \
+                or not kept.is_contiguous() or tokens.dtype != torch.int32:
+            raise KernelError("bigram_embed: residual float32 [T, n], table [buckets + 1, n], kept int32 [slots, 1]")
+        self.launches += 1
+        _check(self.lib.chibi_bigram_embed(_ptr(residual), _ptr(table), _code(table), _ptr(tokens), _ptr(positions),
+                                           _ptr(seq_of_token), _ptr(q_start), _ptr(state_slots), _ptr(kept), T, n,
+                                           table.shape[0] - 1, int(mul_prev), int(mul_cur), self._stream()),
+               "bigram_embed")
+
+    def stream_enter(self, x: torch.Tensor, x0: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> None:
+        """x += x0 + vec (float32; x0 [T, n] and the row vector vec [n] may each be None)."""
+        _need_cuda(x, x0, vec)
+        T, n = x.shape
+        if x.dtype != torch.float32 or not x.is_contiguous() \
+                or (x0 is not None and (x0.dtype != torch.float32 or x0.shape != x.shape or not x0.is_contiguous())) \
+                or (vec is not None and (vec.dtype != torch.float32 or vec.shape != (n,) or not vec.is_contiguous())):
+            raise KernelError("stream_enter: contiguous float32 x [T, n], x0 [T, n], vec [n]")
+        self.launches += 1
+        _check(self.lib.chibi_stream_enter(_ptr(x), _ptr(x0), _ptr(vec), T, n, self._stream()), "stream_enter")
+
+    def add_weighted(self, acc: torch.Tensor, a: torch.Tensor, wa: float, b: Optional[torch.Tensor] = None,
+                     wb: float = 0.0) -> None:
+        """acc += wa * a + wb * b (all contiguous float32 of one size)."""
+        _need_cuda(acc, a, b)
+        for t in (acc, a, b):
+            if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != acc.numel()):
+                raise KernelError("add_weighted: contiguous float32 arrays of one size")
+        self.launches += 1
+        _check(self.lib.chibi_add_weighted(_ptr(acc), _ptr(a), float(wa), _ptr(b), float(wb), acc.numel(),
+                                           self._stream()), "add_weighted")
+
+    def heads_prepare_append(self, proj: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                             v_cache: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                             q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                             inv_freq: Optional[torch.Tensor], rotary_dim: int, positions: torch.Tensor,
+                             seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], nq: int, nk: int,
+                             nv: int, d: int, dv: int, page_size: int,
+                             seq_rows: Optional[torch.Tensor] = None) -> None:
+        """Per head of a row q | k | v ([T, >= nq d + nk d + nv dv]; [T, >= nq d] without a cache):
+        + bias (float32 over the row, or None); q and k heads divided by their root mean square and
+        multiplied by ``q_norm`` / ``k_norm`` (float32 [d], both or none); the first ``rotary_dim``
+        features rotated; q -> q_out, k -> [pages, nk, page, d], v -> [pages, nv, page, dv]."""
+        _need_cuda(proj, q_out, k_cache, v_cache, bias, q_norm, k_norm, inv_freq, positions, seq_of_token,
+                   block_table, seq_rows)
+        _rows_contiguous(proj, "heads_prepare_append: proj")
+        T = proj.shape[0]
+        append = k_cache is not None
+        width = nq * d + ((nk * d + nv * dv) if append else 0)
+        if proj.shape[1] < width or not q_out.is_contiguous() or q_out.shape != (T, nq * d) or q_out.dtype != proj.dtype:
+            raise KernelError("heads_prepare_append: proj / q_out shapes or types")
+        if (q_norm is None) != (k_norm is None):
+            raise KernelError("heads_prepare_append: give both norm weights or none")
+        for t, size, what in ((bias, width, "bias"), (q_norm, d, "q_norm"), (k_norm, d, "k_norm")):
+            if t is not None and (t.dtype != torch.float32 or t.numel() < size or not t.is_contiguous()):
+                raise KernelError(f"heads_prepare_append: {what} must be contiguous float32 of {size} values")
+        if rotary_dim and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rotary_dim // 2):
+            raise KernelError("heads_prepare_append: inv_freq must hold rotary_dim/2 float32 values")
+        num_pages = table_stride = 0
+        if append:
+            if (v_cache is None or not k_cache.is_contiguous() or not v_cache.is_contiguous()
+                    or tuple(k_cache.shape[1:]) != (nk, page_size, d)
+                    or tuple(v_cache.shape) != (k_cache.shape[0], nv, page_size, dv) or v_cache.dtype != k_cache.dtype):
+                raise KernelError(f"heads_prepare_append: cache shapes {tuple(k_cache.shape)}")
+            num_pages = k_cache.shape[0]
+            _rows_contiguous(block_table, "heads_prepare_append: block_table")
+            table_stride = block_table.stride(0)
+        self.launches += 1
+        _check(self.lib.chibi_heads_prepare_append(
+            _ptr(proj), _code(proj), proj.stride(0), _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps),
+            _ptr(inv_freq) if rotary_dim else None, int(rotary_dim), _ptr(positions), _ptr(seq_of_token),
+            _ptr(seq_rows), _ptr(block_table), table_stride, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+            _code(k_cache) if append else F32, T, nq, nk, nv, d, dv, page_size, num_pages, _ptr(self.error),
+            self._stream()), "heads_prepare_append")
+
+    def differential_combine(self, att: torch.Tensor, gate: Optional[torch.Tensor], lam: float, eps: float,
+                             out_scale: float, out: torch.Tensor, heads: int, dv: int, group: int) -> None:
+        """Per head h of att (float32 [T, 2 * heads * dv]; the ``group`` heads of a key/value head side
+        by side, first their first maps, then their second ones):
+        o = a1 - lam * a2; out[t, h] = o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate[t, h])."""
+        _need_cuda(att, gate, out)
+        T = att.shape[0]
+        if att.dtype != torch.float32 or not att.is_contiguous() or att.shape != (T, heads * 2 * dv) \
+                or out.shape != (T, heads * dv) or not out.is_contiguous():
+            raise KernelError("differential_combine: att float32 [T, 2 heads dv] and out [T, heads dv]")
+        if gate is not None:
+            _rows_contiguous(gate, "differential_combine: gate")
+            if gate.shape != (T, heads) or gate.dtype != out.dtype:
+                raise KernelError("differential_combine: gate [T, heads] of out's type")
+        self.launches += 1
+        _check(self.lib.chibi_differential_combine(_ptr(att), _ptr(gate), _code(out),
+                                                   gate.stride(0) if gate is not None else 0, float(lam), float(eps),
+                                                   float(out_scale), _ptr(out), T, heads, dv, int(group),
+                                                   self._stream()), "differential_combine")
+
+    def causal_conv(self, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                    history: torch.Tensor, out: torch.Tensor, q_start: torch.Tensor, state_slots: torch.Tensor,
+                    max_q_len: int, activation: Optional[str] = None, weight_t: Optional[torch.Tensor] = None) -> None:
+        """out_t = act(bias + sum_j weight[:, j] * x_(t - taps + 1 + j)) per channel along each sequence
+        of the step (zeros before a sequence's start); ``history`` as for ``short_conv``."""
+        _need_cuda(x, weight, bias, history, out, q_start, state_slots, weight_t)
+        _rows_contiguous(x, "causal_conv: x")
+        _rows_contiguous(out, "causal_conv: out")
+        T, D = x.shape
+        taps = weight.shape[1]
+        if weight.shape != (D, taps) or weight.dtype != torch.float32 or not weight.is_contiguous() \
+                or out.shape != x.shape or out.dtype != x.dtype or history.dtype != x.dtype \
+                or not history.is_contiguous() or tuple(history.shape[1:]) != (max(taps - 1, 1), D) \
+                or (bias is not None and (bias.dtype != torch.float32 or bias.shape != (D,) or not bias.is_contiguous())) \
+                or (activation is not None and activation not in self.ACTIVATIONS):
+            raise KernelError("causal_conv: weight float32 [D, taps], bias float32 [D], history [slots, taps - 1, D]")
+        if weight_t is not None and (weight_t.dtype != torch.float32 or weight_t.shape != (taps, D)
+                                     or not weight_t.is_contiguous()):
+            raise KernelError("causal_conv: weight_t must be the weight transposed, contiguous float32 [taps, D]")
+        self.launches += 1
+        _check(self.lib.chibi_causal_conv(_ptr(x), _code(x), x.stride(0), _ptr(weight), _ptr(weight_t), _ptr(history),
+                                          _ptr(out), out.stride(0), _ptr(q_start), _ptr(state_slots),
+                                          state_slots.numel(), int(max_q_len), D, taps, _ptr(bias),
+                                          self.ACTIVATIONS[activation] if activation is not None else -1, 0,
+                                          self._stream()), "causal_conv")
+
+    def state_space_scan(self, xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                         skip: torch.Tensor, state: torch.Tensor, y: torch.Tensor, q_start: torch.Tensor,
+                         state_slots: torch.Tensor, heads: int, groups: int, e: int, n: int) -> None:
+        """Per head h (group g = h // (heads / groups)) over the step's tokens of every sequence:
+        step = softplus(dt[t, h] + dt_bias[h]); S <- exp(-exp(a_log[h]) * step) S + step * B_t x_t^T;
+        y_t = S^T C_t + skip[h] * x_t.  xbc [T, heads e + 2 groups n] holds x | B | C; ``state`` float32
+        [slots, heads, e, n] (value column first) is read and left per request; y float32 [T, heads e]."""
+        _need_cuda(xbc, dt, dt_bias, a_log, skip, state, y, q_start, state_slots)
+        _rows_contiguous(xbc, "state_space_scan: xbc")
+        _rows_contiguous(dt, "state_space_scan: dt")
+        T = xbc.shape[0]
+        if xbc.shape[1] != heads * e + 2 * groups * n or dt.shape != (T, heads) or dt.dtype != xbc.dtype \
+                or state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, e, n) \
+                or y.dtype != torch.float32 or y.shape != (T, heads * e) or not y.is_contiguous():
+            raise KernelError("state_space_scan: shapes or types")
+        for t in (dt_bias, a_log, skip):
+            if t.dtype != torch.float32 or t.shape != (heads,) or not t.is_contiguous():
+                raise KernelError("state_space_scan: dt_bias, a_log and skip are contiguous float32 [heads]")
+        self.launches += 1
+        _check(self.lib.chibi_state_space_scan(_ptr(xbc), _code(xbc), xbc.stride(0), _ptr(dt), dt.stride(0),
+                                               _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state), _ptr(y),
+                                               _ptr(q_start), _ptr(state_slots), state_slots.numel(), heads, groups,
+                                               e, n, self._stream()), "state_space_scan")
+
+    def gated_group_rms(self, y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, parts: int,
+                        out: torch.Tensor) -> None:
+        """v = y * silu(z); out = v / sqrt(mean(v^2 over each of ``parts`` equal parts) + eps) * weight."""
+        _need_cuda(y, z, weight, out)
+        _rows_contiguous(z, "gated_group_rms: z")
+        T, W = y.shape
+        if y.dtype != torch.float32 or not y.is_contiguous() or z.shape != y.shape or W % parts != 0 \
+                or weight.dtype != torch.float32 or weight.shape != (W,) or not weight.is_contiguous() \
+                or out.shape != y.shape or not out.is_contiguous() or out.dtype != z.dtype:
+            raise KernelError("gated_group_rms: y float32 [T, W], z [T, W], weight float32 [W], out [T, W] of z's type")
+        self.launches += 1
+        _check(self.lib.chibi_gated_group_rms(_ptr(y), _ptr(z), _code(z), z.stride(0), _ptr(weight), float(eps),
+                                              _ptr(out), T, W, int(parts), self._stream()), "gated_group_rms")
+
+    def clamped_swish_gate(self, gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float) -> None:
+        """g = min(gate, limit), u = clamp(up, -limit, limit); out = g * sigmoid(slope * g) * (u + 1);
+        gate_up [T, 2 n] holds the gate columns, then the up columns."""
+        _need_cuda(gate_up, out)
+        _rows_contiguous(gate_up, "clamped_swish_gate: gate_up")
+        T, n = out.shape
+        if gate_up.shape != (T, 2 * n) or not out.is_contiguous() or out.dtype != gate_up.dtype:
+            raise KernelError("clamped_swish_gate: gate_up [T, 2 n] and out [T, n] of one type")
+        self.launches += 1
+        _check(self.lib.chibi_clamped_swish_gate(_ptr(gate_up), _code(gate_up), gate_up.stride(0), _ptr(out), T, n,
+                                                 float(limit), float(slope), self._stream()), "clamped_swish_gate")
+
+    def router_choose(self, logits: torch.Tensor, correction: Optional[torch.Tensor], chosen: torch.Tensor,
+                      share: torch.Tensor, group_count: int, group_keep: int, scale: float,
+                      last_choice: Optional[int] = None) -> None:
+        """s = softmax(logits[t]) (float32 [T, n]); choice = s + correction; of ``group_count`` equal
+        groups of neighbours only the ``group_keep`` with the largest best choice stay open;
+        chosen[t] (int32 [T, top]) = the open outputs with the largest choice, largest first, ties to
+        the lower number; share[t] = s[chosen] * scale.  ``last_choice``: numbers above it are written
+        as it (outputs that all name the same thing, such as experts that return their input)."""
+        _need_cuda(logits, correction, chosen, share)
+        _rows_contiguous(logits, "router_choose: logits")
+        T, n = logits.shape
+        top = chosen.shape[1]
+        if logits.dtype != torch.float32 or chosen.dtype != torch.int32 or share.dtype != torch.float32 \
+                or chosen.shape != (T, top) or share.shape != (T, top) or not chosen.is_contiguous() \
+                or not share.is_contiguous() or not (0 < top <= n) \
+                or (correction is not None and (correction.dtype != torch.float32 or correction.shape != (n,)
+                                                or not correction.is_contiguous())):
+            raise KernelError("router_choose: shapes or types")
+        self.launches += 1
+        _check(self.lib.chibi_router_choose(_ptr(logits), logits.stride(0), _ptr(correction), _ptr(chosen),
+                                            _ptr(share), T, n, top, int(group_count), int(group_keep), float(scale),
+                                            n - 1 if last_choice is None else int(last_choice), self._stream()),
+               "router_choose")
+
+    def scaled_add_norm(self, residual: torch.Tensor, delta: torch.Tensor, vec: Optional[torch.Tensor],
+                        norm=None) -> None:
+        """residual += vec * delta (vec float32 [n] or None for ones); then, with ``norm`` = (weight,
+        eps, offset, out): out = residual / rms(residual) * (weight + offset).  One launch."""
+        _need_cuda(residual, delta, vec)
+        T, n = residual.shape
+        if residual.dtype != torch.float32 or not residual.is_contiguous() or delta.dtype != torch.float32 \
+                or delta.shape != residual.shape or not delta.is_contiguous() \
+                or (vec is not None and (vec.dtype != torch.float32 or vec.shape != (n,) or not vec.is_contiguous())):
+            raise KernelError("scaled_add_norm: contiguous float32 residual and delta [T, n], vec [n]")
+        w = out = None
+        eps = offset = 0.0
+        if norm is not None:
+            w, eps, offset, out = norm
+            _need_cuda(w, out)
+            if w.shape != (n,) or not w.is_contiguous() or out.shape != (T, n) or not out.is_contiguous():
+                raise KernelError("scaled_add_norm: shapes of the norm")
+        self.launches += 1
+        _check(self.lib.chibi_scaled_add_norm(_ptr(residual), _ptr(delta), _ptr(vec), _ptr(w),
+                                              _code(w) if w is not None else F32, float(eps), float(offset),
+                                              _ptr(out), _code(out) if out is not None else F32, T, n,
+                                              self._stream()), "scaled_add_norm")
 
     def softcap(self, x: torch.Tensor, cap: float) -> None:
         """x = cap * tanh(x / cap), in place (float32)."""

@@ -25,7 +25,7 @@ RECORD = np.dtype([("unit", "<u4"), ("line", "<u4"), ("block", "<u4"), ("blocks"
                    ("pad", "<u4"), ("start", "<u8"), ("waited", "<u8"), ("end", "<u8"), ("marks", "<u8", (4,))])
 UNITS = {1: "elementwise", 2: "gemm_simt", 3: "gemm_tcgen05", 4: "attention_generic", 5: "sampling",
          6: "attention_mma", 7: "attention_tcgen05", 8: "sequence_ops", 9: "layer_ops", 10: "experts_tcgen05",
-         11: "mixer_ops"}
+         11: "mixer_ops", 12: "hybrid_ops"}
 DEFINE = "CHIBI_TIMELINE"
 
 

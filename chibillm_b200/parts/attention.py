@@ -34,6 +34,15 @@ concatenated heads (``biases``, ``whole_norm_eps``, ``output_gate``) take an ord
 of their own: one product gives q | k | v | gate, one kernel adds the biases,
 normalises, rotates if there is a rotation, writes q and appends k and v, attention
 follows, one kernel multiplies by sigmoid(gate), then the output product.
+
+Several score maps per head (``query_maps``; two maps joined as a1 - lambda a2:
+``differential``), a gate per head (``head_gate``), a bias linear in the distance and
+biases together with a per-head norm take one more order: one product gives
+q | k | v (| the heads' gates); one kernel adds the biases, normalises every q and k
+head with the shared weight, rotates, writes q and appends k and v (the maps of a key
+head are key heads of the cache that share one value head); attention follows, 32-bit
+where maps are to be subtracted; one kernel joins the maps, normalises and gates; then
+the output product.
 """
 from __future__ import annotations
 
@@ -58,14 +67,39 @@ class PagedAttention(Mixer):
         self.k_norm: torch.Tensor = None
         self.distance_r1: torch.Tensor = None
         self.distance_r2: torch.Tensor = None
-        if spec.distance_bias not in (None, "log"):
-            raise ValueError(f"distance bias '{spec.distance_bias}' is not supported (None or 'log')")
+        if spec.distance_bias not in (None, "log", "linear"):
+            raise ValueError(f"distance bias '{spec.distance_bias}' is not supported (None, 'log' or 'linear')")
+        self.maps = int(getattr(spec, "query_maps", 1))
+        # the order of the module's last paragraph
+        self.prepared = (self.maps > 1 or getattr(spec, "head_gate", False) or spec.distance_bias == "linear"
+                         or (spec.biases and spec.qk_norm is not None))
+        if self.prepared:
+            if spec.tied_values or spec.unit_norm_eps is not None or spec.whole_norm_eps is not None \
+                    or spec.output_gate or spec.softcap is not None or not spec.own_kv:
+                raise ValueError("score maps, a gate per head, a linear distance bias and biases with a per-head "
+                                 "norm are not combined with tied values, a norm after the rotation or over the "
+                                 "whole projection, a gate per feature, a soft cap or a borrowed cache")
+            if getattr(spec, "differential", None) is not None and self.maps != 2:
+                raise ValueError("differential attention has two score maps per head")
+            if self.maps > 1 and getattr(spec, "differential", None) is None:
+                raise ValueError("several score maps need a rule that joins them (differential)")
+            if getattr(spec, "head_gate", False) and self.maps == 1:
+                raise ValueError("a gate per head is applied where the score maps are joined")
+            if self.maps > 1 and spec.biases:
+                raise ValueError("several score maps are not combined with biases")
+        self.lam = 0.0
+        self.slopes: torch.Tensor = None
         self.kv_arrays = 1 if spec.tied_values else 2
         self.value_dim = spec.head_dim if spec.value_dim is None else spec.value_dim
         if spec.tied_values and self.value_dim != spec.head_dim:
             raise ValueError("values tied to the keys have the keys' size")
         if spec.unit_norm_eps is not None and spec.qk_norm is not None:
             raise ValueError("a norm of q and k comes either before the rotation (qk_norm) or after it (unit_norm_eps)")
+        if self.prepared:
+            self.rotate_then_norm = self.bias_norm_gate = False
+            self.bias = self.sink = None
+            self.gate_columns = 0
+            return
         # the plain order of kernels (see the module's text)
         self.rotate_then_norm = (spec.unit_norm_eps is not None or self.value_dim != spec.head_dim
                                  or getattr(self.position, "amplitude", 1.0) != 1.0)
@@ -87,14 +121,19 @@ class PagedAttention(Mixer):
     # ---- weights
     def expected_tensors(self) -> List[TensorSpec]:
         s = self.spec
-        qw, kw = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        qw, kw = s.num_heads * self.maps * s.head_dim, s.num_kv_heads * self.maps * s.head_dim
         out = [TensorSpec(self.names["q_proj"], (qw, s.hidden_size))]
         if s.own_kv:
             out.append(TensorSpec(self.names["k_proj"], (kw, s.hidden_size)))
             if not s.tied_values:
                 out.append(TensorSpec(self.names["v_proj"], (s.num_kv_heads * self.value_dim, s.hidden_size)))
         out.append(TensorSpec(self.names["o_proj"], (s.hidden_size, s.num_heads * self.value_dim)))
-        if s.distance_bias is not None:
+        if getattr(s, "differential", None) is not None:
+            out += [TensorSpec(self.names[r], (s.head_dim,), init=("normal", 0.0, 0.1))
+                    for r in ("lambda_q1", "lambda_k1", "lambda_q2", "lambda_k2")]
+        if getattr(s, "head_gate", False):
+            out.append(TensorSpec(self.names["head_gate"], (s.num_heads, s.hidden_size)))
+        if s.distance_bias == "log":
             out += [TensorSpec(self.names["distance_r1"], (s.num_heads,), init=("uniform", 0.0, 2.0)),
                     TensorSpec(self.names["distance_r2"], (s.num_heads,), init=("uniform", 0.1, 0.5))]
         if s.qk_norm is not None:
@@ -122,7 +161,28 @@ class PagedAttention(Mixer):
         if self.spec.output_gate:
             roles = roles + ("g_proj",)
             self.gate_columns = tensors[self.names["g_proj"]].shape[0]
+        if getattr(self.spec, "head_gate", False):
+            roles = roles + ("head_gate",)
+            self.gate_columns = tensors[self.names["head_gate"]].shape[0]
+        if getattr(self.spec, "differential", None) is not None:
+            lq1, lk1, lq2, lk2 = (tensors[self.names[r]].float() for r in ("lambda_q1", "lambda_k1", "lambda_q2",
+                                                                              "lambda_k2"))
+            # one number for the layer, made once in 32-bit
+            self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum())
+                             + torch.tensor(float(self.spec.differential)))
+        if self.spec.distance_bias == "linear":
+            H = self.spec.num_heads
+            self.slopes = torch.tensor([2.0 ** (-float(self.spec.distance_slope_bits) * (h + 1) / H)
+                                        for h in range(H)], dtype=torch.float32,
+                                       device=tensors[self.names["q_proj"]].device)
         mats = [tensors[self.names[r]] for r in roles]
+        if self.maps > 1:
+            # Query rows come head by head, a head's maps side by side; a key head of the cache is one map
+            # of one key/value head.  The attention kernels give query head i key head i // (heads per key
+            # head), so the rows are put in the order (key/value head, map, head of the group).
+            s, M = self.spec, self.maps
+            G, R, d = s.num_kv_heads, s.num_heads // s.num_kv_heads, s.head_dim
+            mats[0] = mats[0].view(G, R, M, d, -1).permute(0, 2, 1, 3, 4).reshape(mats[0].shape)
         self.qkv = torch.cat([m.to(mats[0].dtype) for m in mats], dim=0).contiguous()
         if self.spec.sink:
             self.sink = tensors[self.names["sink"]].float().contiguous()
@@ -132,13 +192,15 @@ class PagedAttention(Mixer):
         if self.spec.whole_norm_eps is not None:
             self.q_norm = tensors[self.names["q_norm"]].float().contiguous()
             self.k_norm = tensors[self.names["k_norm"]].float().contiguous() if self.spec.own_kv else None
-        if self.spec.distance_bias is not None:
+        if self.spec.distance_bias == "log":
             self.distance_r1 = tensors[self.names["distance_r1"]].float().contiguous()
             self.distance_r2 = tensors[self.names["distance_r2"]].float().contiguous()
         self.o_proj = tensors[self.names["o_proj"]].contiguous()
         if self.spec.qk_norm is not None:
             self.q_norm = tensors[self.names["q_norm"]].contiguous()
             self.k_norm = tensors[self.names["k_norm"]].to(self.q_norm.dtype).contiguous()
+            if self.prepared:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
 
     # ---- cache
     accepts_scaled_rows = True       # x goes to the q | k | v product and nowhere else
@@ -146,13 +208,16 @@ class PagedAttention(Mixer):
     def cache_need(self):
         s = self.spec
         kept = s.window if isinstance(s.cache_window, str) else s.cache_window
-        return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=kept,
+        return PagedKVNeed(num_kv_heads=s.num_kv_heads * self.maps, head_dim=s.head_dim, window=kept,
                            tied_values=s.tied_values,
-                           value_dim=self.value_dim if self.value_dim != s.head_dim else None)
+                           value_dim=self.value_dim if self.value_dim != s.head_dim else None,
+                           value_heads=s.num_kv_heads if self.maps > 1 else None)
 
     def launch_key(self, ctx):
         if self.position.fused_rotation() is None:
             return None                      # an encoding of its own: nothing is promised
+        if self.prepared:
+            return ()                        # the plain attention kernel: nothing is decided on the host
         k = self.runtime.kernels
         splits = getattr(k, "decode_attention_splits", None)
         if splits is None:
@@ -170,6 +235,8 @@ class PagedAttention(Mixer):
         writes = cache.writes
         if writes and not s.own_kv:
             raise ValueError("a layer without key and value projections must read another run step's cache")
+        if self.prepared:
+            return self._prepared_attend(x, residual, ctx, cache)
         if self.bias_norm_gate:
             return self._bias_norm_gate_attend(x, residual, ctx, cache)
         if self.rotate_then_norm:
@@ -248,6 +315,53 @@ class PagedAttention(Mixer):
                               ctx.tables[cache.group] if writes else None, nq, nkv, d, dv, cache.page_size,
                               ctx.seq_rows)
         return self._attend(residual, ctx, cache)
+
+    def _prepared_attend(self, x, residual, ctx, cache):
+        """q | k | v (| gates) from one product; biases, per-head norm, rotation and append in one
+        kernel; attention with the maps of a head as heads of their own that share the head's
+        values; the maps joined, normalised and gated; the output product."""
+        s, rt = self.spec, self.runtime
+        k = rt.kernels
+        T = x.shape[0]
+        M = self.maps
+        nq, nk, nv, d, dv = s.num_heads * M, s.num_kv_heads * M, s.num_kv_heads, s.head_dim, self.value_dim
+        inv_freq, rotary_dim = self.position.fused_rotation() or (None, 0)
+        if inv_freq is None and s.position.kind != "none":
+            raise ValueError("this order of kernels needs a rotation that the kernels apply")
+        proj = ctx.workspace.get("attn.qkv", (T, self.qkv.shape[0]), rt.dtype)
+        k.linear(x, self.qkv, proj)
+        q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
+        norm = s.qk_norm
+        table = ctx.tables[cache.group]
+        k.heads_prepare_append(proj, q, cache.keys, cache.values, self.bias,
+                               self.q_norm if norm is not None else None, self.k_norm if norm is not None else None,
+                               norm.eps if norm is not None else 0.0, inv_freq,
+                               rotary_dim if inv_freq is not None else 0, ctx.positions, ctx.seq_of_token, table,
+                               nq, nk, nv, d, dv, cache.page_size, ctx.seq_rows)
+        extra = {}
+        if s.chunk is not None:
+            extra["chunk"] = s.chunk
+        if dv != d:
+            extra["value_dim"] = dv
+        if s.sink:
+            extra["sink"] = self.sink
+        if s.distance_bias == "linear":
+            extra["distance_bias"] = (self.slopes, None)
+        if M > 1:
+            extra["kv_share"] = M
+        joined = M > 1
+        att = ctx.workspace.get("attn.maps" if joined else "attn.out", (T, nq * dv),
+                                torch.float32 if joined else rt.dtype)
+        k.attention(q, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len, ctx.seq_of_token,
+                    ctx.positions, nq, nk, d, cache.page_size, s.scale, s.window, ctx.max_q_len, ctx.max_ctx_len,
+                    ctx.min_q_len, ctx.seq_rows, **extra)
+        if joined:
+            out = ctx.workspace.get("attn.out", (T, s.num_heads * dv), rt.dtype)
+            gate = proj[:, proj.shape[1] - self.gate_columns:] if self.gate_columns else None
+            k.differential_combine(att, gate, self.lam, s.differential_eps, 1.0 - float(s.differential), out,
+                                   s.num_heads, dv, s.num_heads // s.num_kv_heads)
+            att = out
+        return k.linear(att, self.o_proj, residual, residual=residual, defer=True)
 
     def _bias_norm_gate_attend(self, x, residual, ctx, cache):
         """q | k | v | gate from one product; biases, the norm over the whole q and k,

@@ -50,13 +50,16 @@ class PagedKVNeed:
     """Keys and values of every position, in pages; ``window`` None = all keys
     stay, an integer = only that many most recent ones are ever read.
     ``tied_values``: the values are the keys; the pool holds one array.
-    ``value_dim`` (None: ``head_dim``): the size of a value head."""
+    ``value_dim`` (None: ``head_dim``): the size of a value head.
+    ``value_heads`` (None: ``num_kv_heads``): the number of value heads where several
+    key heads share one."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     tied_values: bool = False
     value_dim: Optional[int] = None
+    value_heads: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -187,6 +190,11 @@ class Adapter(Part):
     ``ctx.shared["embedding output"]``."""
 
     needs_embedding_output = False
+
+    def cache_need(self):
+        """What an input adapter keeps per request (a FixedStateNeed) or None; with a need its
+        ``forward`` gets the view as ``cache=``."""
+        return None
 
     def forward(self, x: torch.Tensor, ctx, turn: int = 0) -> None:
         raise NotImplementedError

@@ -3,7 +3,11 @@ residual += feed_forward(norm(residual)); the residual itself is never
 normalised in place (src/qwen/qwen_layer.cc:124-146).  Two options of the
 layer's spec: a short convolution over time between the first norm and the
 mixer (it keeps its last inputs per request, so the block then has two cache
-needs), and no feed-forward at all.
+needs), and no feed-forward at all.  With ``layer_scale`` each sublayer's result is
+multiplied feature by feature by a learned vector before it joins the residual: the
+sublayer then adds into a 32-bit array of its own, and one kernel adds vector * array
+to the residual and writes the next norm's output (the block leaves that kernel
+pending, as it leaves a product pending otherwise).
 
 "parallel": one norm whose output both branches read,
 residual += scale * (mixer(norm(residual)) + feed_forward(norm(residual))), then an
@@ -31,6 +35,22 @@ from .short_conv import ShortConv
 from .token_input import TokenInput
 
 
+class ScaledSum:
+    """What a sublayer with a scale per feature leaves pending: its sum, still to be multiplied
+    by the vector and added to the residual; the norm that follows can be done on the way."""
+
+    def __init__(self, kernels, delta: torch.Tensor, vec: torch.Tensor):
+        self.kernels, self.delta, self.vec = kernels, delta, vec
+
+    def add_into(self, residual: torch.Tensor) -> None:
+        self.kernels.scaled_add_norm(residual, self.delta, self.vec)
+
+    def finish_with_norm(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, offset: float,
+                         out: torch.Tensor, scaled_ok: bool):
+        self.kernels.scaled_add_norm(residual, self.delta, self.vec, norm=(weight, eps, offset, out))
+        return out
+
+
 class PreNormBlock(Block):
     def __init__(self, layer, runtime: Runtime):
         self.layer = layer
@@ -45,16 +65,38 @@ class PreNormBlock(Block):
             self.feed_forward = make_feed_forward(layer.feed_forward, names, runtime)
         self._parts = tuple(p for p in (self.mixer_norm, self.mixer_conv, self.mixer, self.feed_forward_norm,
                                         self.feed_forward) if p is not None)
+        self.scale_names = None
+        self.mixer_scale: torch.Tensor = None
+        self.feed_forward_scale: torch.Tensor = None
+        if getattr(layer, "layer_scale", False):
+            self.scale_names = (names["mixer_scale"],
+                                names["feed_forward_scale"] if self.feed_forward is not None else None)
 
     def expected_tensors(self) -> List[TensorSpec]:
         out: List[TensorSpec] = []
         for p in self._parts:
             out.extend(p.expected_tensors())
+        if self.scale_names is not None:
+            out += [TensorSpec(n, (self.layer.mixer_norm.size,)) for n in self.scale_names if n is not None]
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for p in self._parts:
             p.bind(tensors)
+        if self.scale_names is not None:
+            self.mixer_scale = tensors[self.scale_names[0]].float().contiguous()
+            if self.scale_names[1] is not None:
+                self.feed_forward_scale = tensors[self.scale_names[1]].float().contiguous()
+
+    def _scaled(self, run, vec: torch.Tensor, residual: torch.Tensor, ctx, tag: str) -> ScaledSum:
+        """Runs a sublayer into a 32-bit array of its own; what joins the residual is vec * that."""
+        k = self.runtime.kernels
+        delta = ctx.workspace.get("block.delta." + tag, tuple(residual.shape), torch.float32)
+        k.zero(delta)
+        left = run(delta)
+        if left is not None:
+            left.add_into(delta)
+        return ScaledSum(k, delta, vec)
 
     def cache_need(self):
         if self.mixer_conv is None:
@@ -76,11 +118,19 @@ class PreNormBlock(Block):
             mixed = ctx.workspace.get("block.conv", tuple(residual.shape), self.runtime.dtype)
             conv.forward(normed, mixed, ctx, conv_state)
             normed = mixed
-        pending = self.mixer.forward(normed, residual, ctx, cache)
+        if self.scale_names is not None:
+            pending = self._scaled(lambda acc: self.mixer.forward(normed, acc, ctx, cache), self.mixer_scale,
+                                   residual, ctx, "mixer")
+        else:
+            pending = self.mixer.forward(normed, residual, ctx, cache)
         if self.feed_forward is None:
             return pending
         normed = self.feed_forward_norm.forward_fused(residual, pending, x, self.feed_forward.accepts_scaled_rows)
-        return self.feed_forward.forward(x if normed is None else normed, residual, ctx)
+        normed = x if normed is None else normed
+        if self.scale_names is not None:
+            return self._scaled(lambda acc: self.feed_forward.forward(normed, acc, ctx), self.feed_forward_scale,
+                                residual, ctx, "ff")
+        return self.feed_forward.forward(normed, residual, ctx)
 
 
 class LayerEnd:

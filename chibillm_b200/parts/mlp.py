@@ -15,7 +15,12 @@ work; nothing is read on the host, so a decode step can be captured.
 token by a router: the ``top`` largest of z = W_router x (32-bit), weighted by the
 softmax over the chosen logits.  One kernel picks and weighs, the pairs are sorted
 by expert on the device by the kernel that sorts a table's choices, and the same
-two products over tiles of one expert's rows do the work."""
+two products over tiles of one expert's rows do the work.  Options: gated experts;
+scores from a softmax over all router outputs, chosen by score plus a correction
+within the best groups of outputs and weighted by the plain score times a constant;
+experts without tensors that return their input (their pairs are sorted into a bucket
+of their own whose rows are copies of the tokens' inputs, so the same combination
+weighs them); one more gated expert that every token uses."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -27,8 +32,10 @@ from .base import FeedForward, Runtime, TensorSpec, register_feed_forward
 
 class GatedMLP(FeedForward):
     def __init__(self, spec, names: Dict[str, str], runtime: Runtime):
-        if spec.activation not in ("silu", "gelu_tanh"):
+        if spec.activation not in ("silu", "gelu_tanh", "swish_clamped"):
             raise ValueError(f"activation '{spec.activation}' is not supported by gated_mlp")
+        if spec.activation == "swish_clamped" and (spec.biases or not spec.limit > 0):
+            raise ValueError("gated_mlp: the clamped gate has a positive limit and no biases")
         self.spec = spec
         self.plain_swiglu = spec.activation == "silu" and not spec.biases
         self.bias_gate_up: torch.Tensor = None
@@ -78,7 +85,10 @@ class GatedMLP(FeedForward):
         if not self.plain_swiglu:
             gate_up = ctx.workspace.get("mlp.gate_up", (T, 2 * inter), self.runtime.dtype)
             k.linear(x, self.gate_up, gate_up)
-            k.gated_activation(gate_up, self.bias_gate_up, act, self.spec.activation)
+            if self.spec.activation == "swish_clamped":
+                k.clamped_swish_gate(gate_up, act, self.spec.limit, self.spec.gate_slope)
+            else:
+                k.gated_activation(gate_up, self.bias_gate_up, act, self.spec.activation)
             if self.bias_down is not None:
                 k.add_row_vector(residual, self.bias_down)
             return k.linear(act, self.down, residual, residual=residual, defer=True)
@@ -265,33 +275,78 @@ class RoutedExperts(FeedForward):
     def __init__(self, spec, names: Dict[str, str], runtime: Runtime):
         if spec.activation not in self.ACTIVATIONS:
             raise ValueError(f"activation '{spec.activation}' is not supported by routed_experts")
-        if not (0 < spec.top <= spec.num_experts):
-            raise ValueError("routed_experts: 0 < top <= num_experts is required")
+        self.outputs = spec.num_experts + spec.identity_experts
+        if not (0 < spec.top <= self.outputs):
+            raise ValueError("routed_experts: 0 < top <= num_experts (+ identity_experts) is required")
+        if spec.scores not in ("softmax_top", "softmax_all"):
+            raise ValueError(f"routed_experts: scores '{spec.scores}' is not supported")
+        if spec.scores == "softmax_top" and (spec.correction or spec.group_count != 1 or spec.identity_experts
+                                             or spec.weight_scale != 1.0):
+            raise ValueError("routed_experts: corrections, groups, identity experts and a weight scale belong "
+                             "to scores 'softmax_all'")
+        if self.outputs % spec.group_count != 0 or not (0 < spec.group_keep <= spec.group_count) \
+                or spec.top > (self.outputs // spec.group_count) * spec.group_keep:
+            raise ValueError("routed_experts: the router's outputs must form equal groups whose kept ones hold "
+                             "at least top outputs")
         self.spec = spec
         self.names = names
         self.runtime = runtime
-        self.router: torch.Tensor = None        # [experts, hidden]
-        self.up: torch.Tensor = None            # [experts, ff, hidden]
+        self.router: torch.Tensor = None        # [outputs, hidden]
+        self.correction: torch.Tensor = None    # [outputs], 32-bit
+        self.up: torch.Tensor = None            # [experts, ff, hidden]; gated: [experts, 2 ff, hidden]
         self.down: torch.Tensor = None          # [experts, hidden, ff]
+        self.interleaved = False
+        self.shared = None
+        if spec.shared_size:
+            from ..config.spec import GatedMLPSpec
+            self.shared = GatedMLP(GatedMLPSpec(kind="gated_mlp", hidden_size=spec.hidden_size,
+                                                intermediate_size=spec.shared_size, activation=spec.activation),
+                                   {"gate_proj": names["shared_gate"], "up_proj": names["shared_up"],
+                                    "down_proj": names["shared_down"]}, runtime)
 
     def _name(self, role: str, e: int) -> str:
         return self.names[role].replace("{e}", str(e))
 
     def expected_tensors(self) -> List[TensorSpec]:
         s = self.spec
-        out = [TensorSpec(self.names["router"], (s.num_experts, s.hidden_size), init=("normal", 0.0, 0.5))]
+        out = [TensorSpec(self.names["router"], (self.outputs, s.hidden_size), init=("normal", 0.0, 0.5))]
+        if s.correction:
+            out.append(TensorSpec(self.names["correction"], (self.outputs,), init=("normal", 0.0, 0.02)))
         for e in range(s.num_experts):
+            if s.gated:
+                out.append(TensorSpec(self._name("expert_gate", e), (s.intermediate_size, s.hidden_size)))
             out += [TensorSpec(self._name("expert_up", e), (s.intermediate_size, s.hidden_size)),
                     TensorSpec(self._name("expert_down", e), (s.hidden_size, s.intermediate_size))]
+        if self.shared is not None:
+            out += self.shared.expected_tensors()
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
         self.router = tensors[self.names["router"]].contiguous()
+        if s.correction:
+            self.correction = tensors[self.names["correction"]].float().contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors)
         first = tensors[self._name("expert_up", 0)]
-        self.up = torch.stack([tensors[self._name("expert_up", e)].to(first.dtype) for e in range(s.num_experts)])
-        self.down = torch.stack([tensors[self._name("expert_down", e)].to(first.dtype) for e in range(s.num_experts)])
-        self.up, self.down = self.up.contiguous(), self.down.contiguous()
+        # experts that return their input: one more bucket of the route, behind the experts with tensors; the
+        # stacked matrices get a stand-in of zeros there, so that every expert number of the route is in bounds
+        E = s.num_experts + (1 if s.identity_experts else 0)
+        F, D = s.intermediate_size, s.hidden_size
+        fast = getattr(self.runtime.kernels, "expert_tensor_cores", None)
+        self.interleaved = bool(s.gated and fast is not None and fast(first.dtype, D, F))
+        self.up = torch.zeros((E, (2 if s.gated else 1) * F, D), dtype=first.dtype, device=first.device)
+        self.down = torch.zeros((E, D, F), dtype=first.dtype, device=first.device)
+        for e in range(s.num_experts):
+            up = tensors[self._name("expert_up", e)]
+            if not s.gated:
+                self.up[e] = up
+            elif self.interleaved:
+                self.up[e] = self.runtime.kernels.interleave_expert_gate_up(tensors[self._name("expert_gate", e)], up)
+            else:
+                self.up[e, :F] = tensors[self._name("expert_gate", e)]
+                self.up[e, F:] = up
+            self.down[e] = tensors[self._name("expert_down", e)]
 
     def launch_key(self, ctx):
         return ()
@@ -301,16 +356,28 @@ class RoutedExperts(FeedForward):
         k = rt.kernels
         T = x.shape[0]
         pairs = T * s.top
-        logits = ctx.workspace.get("router.logits", (T, s.num_experts), torch.float32)
+        logits = ctx.workspace.get("router.logits", (T, self.outputs), torch.float32)
         k.linear(x, self.router, logits)
         chosen = ctx.workspace.get("router.chosen", (T, s.top), torch.int32)
         share = ctx.workspace.get("router.share", (T, s.top), torch.float32)
-        k.router_top(logits, chosen, share)
-        route = ctx.workspace.get("experts.route", (k.route_words(pairs, s.num_experts),), torch.int32)
+        buckets = self.up.shape[0]
+        extra = {}
+        if s.scores == "softmax_all":
+            k.router_choose(logits, self.correction, chosen, share, s.group_count, s.group_keep, s.weight_scale,
+                            last_choice=buckets - 1)
+            extra = {"gated": s.gated, "interleaved": self.interleaved, "identity": s.identity_experts}
+        else:
+            k.router_top(logits, chosen, share)
+            if s.gated:
+                extra = {"gated": True, "interleaved": self.interleaved}
+        route = ctx.workspace.get("experts.route", (k.route_words(pairs, buckets),), torch.int32)
         act = ctx.workspace.get("experts.act", (pairs, s.intermediate_size), rt.dtype)
         y = ctx.workspace.get("experts.out", (pairs, s.hidden_size), torch.float32)
         sorted_x = ctx.workspace.get("experts.sorted", (pairs, s.hidden_size), rt.dtype)
-        k.chosen_experts(x, chosen, share, self.up, self.down, residual, route, act, y, s.activation, sorted_x)
+        k.chosen_experts(x, chosen, share, self.up, self.down, residual, route, act, y, s.activation, sorted_x,
+                         **extra)
+        if self.shared is not None:
+            return self.shared.forward(x, residual, ctx)
         return None
 
 

@@ -48,6 +48,26 @@ def stretched_inverse_frequencies(spec) -> torch.Tensor:
     return (freq * (ramp / float(spec.scaling_factor) + (1.0 - ramp))).to(torch.float32)
 
 
+def banded_inverse_frequencies(spec) -> torch.Tensor:
+    """The frequencies of a rotation scaled by wavelength (PositionSpec.wavelength_bands): short
+    waves keep their frequency, long ones are divided by the factor, the band between is blended.
+    Made in 64-bit on the host and rounded once."""
+    factor, low, high, original = (float(v) for v in spec.wavelength_bands)
+    n, theta = spec.rotary_dim, float(spec.theta)
+    out = []
+    for j in range(n // 2):
+        f = theta ** (-2.0 * j / n)
+        wave = 2.0 * math.pi / f
+        if wave < original / high:
+            out.append(f)
+        elif wave > original / low:
+            out.append(f / factor)
+        else:
+            s = (original / wave - low) / (high - low)
+            out.append((1.0 - s) * f / factor + s * f)
+    return torch.tensor(out, dtype=torch.float64).to(torch.float32)
+
+
 class RotaryEncoding(PositionEncoding):
     def __init__(self, spec, runtime: Runtime):
         if spec.rotary_dim % 2 != 0 or spec.rotary_dim > spec.head_dim or spec.rotary_dim <= 0:
@@ -55,7 +75,14 @@ class RotaryEncoding(PositionEncoding):
         self.spec = spec
         self.runtime = runtime
         self.amplitude = 1.0
-        if spec.scaling_factor:
+        bands = getattr(spec, "wavelength_bands", None)
+        if bands is not None:
+            if spec.scaling_factor:
+                raise ValueError("a rotation is stretched either by turns (scaling_factor) or by wavelength bands")
+            if len(bands) != 4 or min(bands) <= 0 or bands[1] == bands[2]:
+                raise ValueError("wavelength bands need positive factor, low, high, original and low != high")
+            self.inv_freq = banded_inverse_frequencies(spec).to(runtime.device)
+        elif spec.scaling_factor:
             if spec.scaling_factor <= 0 or spec.original_positions <= 0 or spec.fast_turns <= 0 or spec.slow_turns <= 0:
                 raise ValueError("a stretched rotation needs positive factor, original positions and turn counts")
             self.inv_freq = stretched_inverse_frequencies(spec).to(runtime.device)
@@ -74,7 +101,7 @@ class RotaryEncoding(PositionEncoding):
             return None                      # the table's readers rotate with amplitude one
         s = self.spec
         key = ("rope", float(s.theta), int(s.rotary_dim), float(s.scaling_factor), int(s.original_positions),
-               float(s.fast_turns), float(s.slow_turns))
+               float(s.fast_turns), float(s.slow_turns), tuple(getattr(s, "wavelength_bands", None) or ()))
         table = ctx.shared.get(key)
         if table is None:
             table = ctx.workspace.get("rope.table." + ".".join(str(v) for v in key[1:]),

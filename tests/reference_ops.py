@@ -88,7 +88,8 @@ class ReferenceKernels:
 
     def attention(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token,
                   positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0,
-                  seq_rows=None, softcap=None, distance_bias=None, chunk=None, value_dim=None, sink=None):
+                  seq_rows=None, softcap=None, distance_bias=None, chunk=None, value_dim=None, sink=None,
+                  kv_share=1):
         self._count("attention")
         T = q.shape[0]
         group = nq // nkv
@@ -115,12 +116,15 @@ class ReferenceKernels:
                     sc = softcap * torch.tanh(sc / softcap)
                 if distance_bias is not None:
                     r1, r2 = distance_bias
-                    sc = sc - r1[h].float() * torch.log1p(r2[h].float() * (p - idx).float())
+                    if r2 is None:
+                        sc = sc - r1[h].float() * (p - idx).float()
+                    else:
+                        sc = sc - r1[h].float() * torch.log1p(r2[h].float() * (p - idx).float())
                 if sink is not None:
                     pr = torch.softmax(torch.cat([sc, sink[h].float().reshape(1)]), dim=0)[:-1]
                 else:
                     pr = torch.softmax(sc, dim=0)
-                res[t, h] = pr @ vals[:, g, :]
+                res[t, h] = pr @ vals[:, g // kv_share, :]
         out.copy_(res.reshape(T, nq * dv).to(out.dtype))
 
     # ---- the operations of layer_ops.cu
@@ -326,15 +330,172 @@ class ReferenceKernels:
         chosen.copy_(idx.to(chosen.dtype))
         share.copy_(torch.softmax(best, dim=-1))
 
-    def chosen_experts(self, x, chosen, share, up, down, acc, route, act, y, kind, sorted_x=None):
+    def chosen_experts(self, x, chosen, share, up, down, acc, route, act, y, kind, sorted_x=None, gated=False,
+                       interleaved=False, identity=0):
         self._count("chosen_experts")
+        assert not interleaved
+        F = down.shape[2]
         for t in range(x.shape[0]):
             total = torch.zeros_like(acc[t])
             for s in range(chosen.shape[1]):
                 e = int(chosen[t, s])
-                hidden = self._act(up[e].float() @ x[t].float(), kind).to(x.dtype).float()
-                total += share[t, s] * (down[e].float() @ hidden)
+                if identity and e >= up.shape[0] - 1:
+                    total += share[t, s] * x[t].float()
+                    continue
+                z = up[e].float() @ x[t].float()
+                hidden = (self._act(z[:F], kind) * z[F:]) if gated else self._act(z, kind)
+                total += share[t, s] * (down[e].float() @ hidden.to(x.dtype).float())
             acc[t] += total
+
+    # ---- the operations of hybrid_ops.cu
+    def bigram_embed(self, residual, table, kept, tokens, positions, seq_of_token, q_start, state_slots, mul_prev,
+                     mul_cur):
+        self._count("bigram_embed")
+        buckets = table.shape[0] - 1
+        for s in range(state_slots.numel()):
+            a, b = int(q_start[s]), int(q_start[s + 1])
+            slot = int(state_slots[s])
+            prev = int(kept[slot, 0])
+            for t in range(a, b):
+                tok = int(tokens[t])
+                row = buckets if int(positions[t]) == 0 else (prev * mul_prev + tok * mul_cur) % buckets
+                residual[t] += table[row].float()
+                prev = tok
+            if b > a:
+                kept[slot, 0] = prev
+
+    def stream_enter(self, x, x0, vec):
+        self._count("stream_enter")
+        if x0 is not None:
+            x.add_(x0)
+        if vec is not None:
+            x.add_(vec)
+
+    def add_weighted(self, acc, a, wa, b=None, wb=0.0):
+        self._count("add_weighted")
+        acc.add_(wa * a.view_as(acc))
+        if b is not None:
+            acc.add_(wb * b.view_as(acc))
+
+    def heads_prepare_append(self, proj, q_out, k_cache, v_cache, bias, q_norm, k_norm, eps, inv_freq, rotary_dim,
+                             positions, seq_of_token, block_table, nq, nk, nv, d, dv, page_size, seq_rows=None):
+        self._count("heads_prepare_append")
+        T = proj.shape[0]
+        append = k_cache is not None
+        width = nq * d + ((nk * d + nv * dv) if append else 0)
+        row = proj[:, :width].float()
+        if bias is not None:
+            row = row + bias[:width].float()
+        pos = positions.float()
+
+        def finish(x, w):
+            if w is not None:
+                x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+            if rotary_dim:
+                half = rotary_dim // 2
+                ang = pos[:, None] * inv_freq[:half].float()[None, :]
+                c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                u, v = x[..., :half], x[..., half:rotary_dim]
+                x = torch.cat([u * c - v * s_, v * c + u * s_, x[..., rotary_dim:]], -1)
+            return x
+
+        q_out.copy_(finish(row[:, :nq * d].reshape(T, nq, d), q_norm).reshape(T, nq * d).to(q_out.dtype))
+        if append:
+            k = finish(row[:, nq * d:nq * d + nk * d].reshape(T, nk, d), k_norm)
+            v = row[:, nq * d + nk * d:].reshape(T, nv, dv)
+            seqs = seq_of_token.long()
+            rows = seq_rows.long()[seqs] if seq_rows is not None else seqs
+            pages = block_table[rows, (positions // page_size).long()].long()
+            assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "append outside the pool"
+            slots = (positions % page_size).long()
+            k_cache[pages, :, slots, :] = k.to(k_cache.dtype)
+            v_cache[pages, :, slots, :] = v.to(v_cache.dtype)
+
+    def differential_combine(self, att, gate, lam, eps, out_scale, out, heads, dv, group):
+        self._count("differential_combine")
+        T = att.shape[0]
+        a = att.float().view(T, heads // group, 2, group, dv)
+        o = (a[:, :, 0] - lam * a[:, :, 1]).reshape(T, heads, dv)
+        o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * out_scale
+        if gate is not None:
+            o = o * torch.sigmoid(gate.float())[:, :, None]
+        out.copy_(o.reshape(T, heads * dv).to(out.dtype))
+
+    def causal_conv(self, x, weight, bias, history, out, q_start, state_slots, max_q_len, activation=None,
+                    weight_t=None):
+        self._count("causal_conv")
+        taps = weight.shape[1]
+        keep = taps - 1
+        for s in range(state_slots.numel()):
+            a, b = int(q_start[s]), int(q_start[s + 1])
+            slot = int(state_slots[s])
+            past = history[slot, :keep].float() if keep else x.new_zeros((0, x.shape[1])).float()
+            seq = torch.cat([past, x[a:b].float()], dim=0)
+            y = torch.zeros(b - a, x.shape[1]) + (bias.float() if bias is not None else 0.0)
+            for j in range(taps):
+                y = y + weight[:, j].float() * seq[j:j + (b - a)]
+            out[a:b] = (self._act(y, activation) if activation is not None else y).to(out.dtype)
+            if keep:
+                history[slot, :keep] = seq[seq.shape[0] - keep:].to(history.dtype)
+
+    def state_space_scan(self, xbc, dt, dt_bias, a_log, skip, state, y, q_start, state_slots, heads, groups, e, n):
+        self._count("state_space_scan")
+        inner = heads * e
+        per = heads // groups
+        for s in range(state_slots.numel()):
+            a, b = int(q_start[s]), int(q_start[s + 1])
+            slot = int(state_slots[s])
+            S = state[slot].clone()                              # [heads, e, n]
+            for t in range(a, b):
+                row = xbc[t].float()
+                x = row[:inner].view(heads, e)
+                B = row[inner:inner + groups * n].view(groups, n).repeat_interleave(per, 0)
+                C = row[inner + groups * n:].view(groups, n).repeat_interleave(per, 0)
+                step = torch.nn.functional.softplus(dt[t].float() + dt_bias)
+                decay = torch.exp(-torch.exp(a_log) * step)
+                S = decay[:, None, None] * S + (step[:, None] * x)[:, :, None] * B[:, None, :]
+                y[t] = (torch.einsum("hen,hn->he", S, C) + skip[:, None] * x).reshape(-1)
+            state[slot] = S
+
+    def gated_group_rms(self, y, z, weight, eps, parts, out):
+        self._count("gated_group_rms")
+        T, W = y.shape
+        v = y * torch.nn.functional.silu(z.float())
+        v = v.view(T, parts, W // parts)
+        v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)
+        out.copy_((v.reshape(T, W) * weight).to(out.dtype))
+
+    def clamped_swish_gate(self, gate_up, out, limit, slope):
+        self._count("clamped_swish_gate")
+        n = out.shape[1]
+        g = gate_up[:, :n].float().clamp(max=limit)
+        u = gate_up[:, n:].float().clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(slope * g) * (u + 1.0)).to(out.dtype))
+
+    def router_choose(self, logits, correction, chosen, share, group_count, group_keep, scale, last_choice=None):
+        self._count("router_choose")
+        T, n = logits.shape
+        top = chosen.shape[1]
+        s = torch.softmax(logits.float(), -1)
+        choice = s + correction if correction is not None else s.clone()
+        if group_count > 1 and group_keep < group_count:
+            per = n // group_count
+            best = choice.view(T, group_count, per).max(-1).values
+            kept = best.topk(group_keep, -1).indices
+            allow = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
+            choice = choice.masked_fill(~allow.repeat_interleave(per, 1), float("-inf"))
+        idx = choice.topk(top, -1).indices
+        share.copy_(s.gather(1, idx) * scale)
+        if last_choice is not None:
+            idx = idx.clamp(max=last_choice)
+        chosen.copy_(idx.to(chosen.dtype))
+
+    def scaled_add_norm(self, residual, delta, vec, norm=None):
+        self._count("scaled_add_norm")
+        residual.add_(delta * vec if vec is not None else delta)
+        if norm is not None:
+            w, eps, offset, out = norm
+            self.rmsnorm(residual, w, eps, offset, out)
 
     def side_gate(self, gate, tokens, table, offset, kind):
         e = table[tokens.long(), offset:offset + gate.shape[1]].float()
