@@ -119,7 +119,7 @@ def softmax_attention(q, k, v, scale, mask, bias=None, sink=None):
 
 def mixer_attention_2(h, m, w, p, eps):
     T = h.shape[0]
-    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
+    H, G, d, e = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
     q = (h @ w[p + "q"].T + w[p + "q.b"]).view(T, H, d)
     k = (h @ w[p + "k"].T + w[p + "k.b"]).view(T, G, d)
     v = (h @ w[p + "v"].T + w[p + "v.b"]).view(T, G, e)
@@ -138,7 +138,7 @@ def differential_lambda(m, w, p):
 
 def mixer_attention(h, m, w, p, eps):
     T = h.shape[0]
-    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
+    H, G, d, e = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
     q = (h @ w[p + "q"].T).view(T, H * 2, d)
     k = (h @ w[p + "k"].T).view(T, G * 2, d)
     v = (h @ w[p + "v"].T).view(T, G, e)
@@ -160,7 +160,7 @@ def distance_slopes(H, dtype):
 
 def mixer_biased_sink_attention(h, m, w, p):
     T = h.shape[0]
-    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
+    H, G, d, e = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
     q = (h @ w[p + "q"].T).view(T, H, d)
     k = (h @ w[p + "k"].T).view(T, G, d)
     v = (h @ w[p + "v"].T).view(T, G, e)
@@ -200,7 +200,7 @@ def state_space_scan(x, B, C, dt, A_log, D):
 
 def mixer_state_space(h, m, w, p, eps):
     T = h.shape[0]
-    H, e, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+    H, e, N, G = m["heads"], m["vdim"], m["state"], m.get("groups", 1)
     inner = H * e
     proj = h @ w[p + "in"].T
     z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
@@ -219,7 +219,7 @@ def mixer_state_space(h, m, w, p, eps):
 def mixer_parallel(h, m, w, p, eps):
     left = mixer_biased_sink_attention(h, m["left"], w, p + "left.")
     right = mixer_state_space(h, m["right"], w, p + "right.", eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
 MIXERS = {"attention": mixer_attention, "attention_2": mixer_attention_2, "parallel": mixer_parallel}
@@ -238,26 +238,43 @@ def expert_ff(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def route(h, mlp, w, p):
-    """For every token the chosen outputs of the router and their weights."""
+def _closest_call(sorted_scores, k, largest):
+    """Gap between the k-th and the (k + 1)-th of scores sorted downwards, as a fraction of ``largest``."""
+    if sorted_scores.shape[-1] <= k:
+        return torch.full(sorted_scores.shape[:-1], float("inf"), dtype=sorted_scores.dtype)
+    gap = sorted_scores[..., k - 1] - sorted_scores[..., k]
+    return torch.where(torch.isfinite(gap), gap / largest, torch.full_like(gap, float("inf")))
+
+
+def route(h, mlp, w, p, margins=None):
+    """For every token the chosen outputs of the router and their weights.  ``margins`` [T] is
+    lowered to the smallest gap that decided a choice (between groups or between outputs), as a
+    fraction of the token's largest score."""
     r = mlp["router"]
     n = r["experts"] + r.get("identity", 0)
     s = torch.softmax(h @ w[p + "router"].T, -1)
     choice = s + w[p + "correction"] if (p + "correction") in w else s.clone()
+    largest = s.max(-1).values
     gr = r.get("groups")
-    if gr and gr["count"] > 1:
+    if gr and gr["count"] > 1 and gr["keep"] < gr["count"]:
         per = n // gr["count"]
         best = choice.view(-1, gr["count"], per).max(-1).values
         kept = best.topk(gr["keep"], -1).indices
+        if margins is not None:
+            margins.copy_(torch.minimum(margins, _closest_call(best.sort(-1, descending=True).values, gr["keep"],
+                                                               largest).to(margins.dtype)))
         allow = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
         choice = choice.masked_fill(~allow.repeat_interleave(per, 1), float("-inf"))
     chosen = choice.topk(r["top"], -1).indices
+    if margins is not None:
+        margins.copy_(torch.minimum(margins, _closest_call(choice.sort(-1, descending=True).values, r["top"],
+                                                           largest).to(margins.dtype)))
     return chosen, s.gather(1, chosen) * r.get("scale", 1.0)
 
 
-def moe_ff(h, mlp, w, p):
+def moe_ff(h, mlp, w, p, margins=None):
     r = mlp["router"]
-    chosen, weight = route(h, mlp, w, p)
+    chosen, weight = route(h, mlp, w, p, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, c in zip(chosen[t].tolist(), weight[t]):
@@ -270,8 +287,8 @@ def moe_ff(h, mlp, w, p):
     return out
 
 
-def feed_forward(h, mlp, w, p):
-    return dense_ff(h, mlp, w, p) if mlp["kind"] == "dense" else moe_ff(h, mlp, w, p)
+def feed_forward(h, mlp, w, p, margins=None):
+    return dense_ff(h, mlp, w, p) if mlp["kind"] == "dense" else moe_ff(h, mlp, w, p, margins)
 
 
 # ---------------------------------------------------------------- the model
@@ -288,8 +305,9 @@ def run_order(config):
     return order + [(i, None, False) for i in range(loop["stop"], n)]
 
 
-def forward(tokens, config, w, layers_out=None):
-    """Logits [T, vocab] of one whole sequence."""
+def forward(tokens, config, w, layers_out=None, margins=None):
+    """Logits [T, vocab] of one whole sequence.  ``layers_out``, a list, takes the residual stream
+    after every layer run; ``margins`` [T] the routers' closest calls (see ``route``)."""
     eps = config["norm"]["eps"]
     x0 = embed(tokens, config, w)
     x = x0.clone()
@@ -305,7 +323,7 @@ def forward(tokens, config, w, layers_out=None):
         x = x + y * w[p + "ls1"] if (p + "ls1") in w else x + y
         if layer.get("mlp"):
             h = rms_norm(x, w[p + "norm2"], eps)
-            y = feed_forward(h, layer["mlp"], w, p + "mlp.")
+            y = feed_forward(h, layer["mlp"], w, p + "mlp.", margins)
             x = x + y * w[p + "ls2"] if (p + "ls2") in w else x + y
         if layers_out is not None:
             layers_out.append(x.clone())
