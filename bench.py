@@ -15,8 +15,8 @@ its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
 filled by real prefill steps for the end-to-end run and with random values for
 the device-timed runs (the work of a decode step does not depend on the values).
 
-``--design gitipel`` (or ``fokurax``, ``pitudra``) prints, instead of the record, prefill and decode
-of that design beside Qwen3 (Pitudra: beside Fokurax) at equal layer sizes, with the time of every kernel.
+``--design gitipel`` (or ``fokurax``, ``pitudra``, ``dogetar``) prints, instead of the record, prefill and decode
+of that design beside Qwen3 (Pitudra: beside Fokurax, Dogetar: beside Pitudra) at equal layer sizes, with the time of every kernel.
 
 ``--timeline`` prints, instead of the record, when the CTAs of every kernel of one
 decode step started, waited and ended.  ``--shape`` runs the same at the Qwen3-0.6B or
@@ -442,6 +442,35 @@ def pitudra_config(width, heads, kv_heads, dim, ff, vocab=32768):
             "layers": [recurrent, latent(), attention, latent(1), recurrent, attention]}
 
 
+def dogetar_config(width, heads, kv_heads, dim, ff, vocab=32768):
+    """Four layers, the middle two run twice: six layer runs.  Attention in a window of 1,024 positions
+    with biases, per-head norms and half of every head rotated (banded frequencies), over a dense
+    feed-forward; differential attention (two maps of half a head each, values of a whole head) in
+    blocks of 1,024 positions; attention with a linear distance bias and a sink beside a state-space
+    branch (heads of 64 values over the whole width, a state of 128, eight groups, four taps); the
+    differential layer once more.  The three routed layers have eight experts of half the dense size
+    and two identity experts in two groups of which one is kept, two choices a token, and a shared
+    expert of the same size; a bigram table of 65,521 buckets."""
+    experts = {"kind": "moe", "expert": {"ff": ff // 2}, "shared": {"ff": ff // 2},
+               "router": {"experts": 8, "identity": 2, "top": 2, "scale": 2.0, "groups": {"count": 2, "keep": 1}}}
+    window = {"type": "attention_2", "mlp": {"kind": "dense", "ff": ff, "limit": 7.0},
+              "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                        "mask": {"size": 1024},
+                        "rot": {"base": 1e6, "dims": dim // 2,
+                                "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 4096}}}}
+    diff = {"type": "attention", "mlp": experts,
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5,
+                      "mask": {"size": 1024}, "rot": {"base": 1e6, "dims": dim // 2}, "diff": 0.5}}
+    par = {"type": "parallel", "mlp": experts,
+           "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                              "mask": {"size": 1024}},
+                     "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8},
+                     "left_scale": 0.8, "right_scale": 0.9}}
+    return {"architecture": "Dogetar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
+            "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [window, diff, par, diff]}
+
+
 def qwen3_config_like(width, heads, kv_heads, dim, ff, layers=6, vocab=32768):
     cfg = dict(QWEN3_8B)
     cfg.update(num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
@@ -511,9 +540,12 @@ def measure_design(name, cfg, vocab, prompt_tokens, batch, held, steps, warmup, 
 def compare_designs(sizes, prompt_tokens, batch, held, steps, warmup, design="gitipel"):
     """Another design beside Qwen3 at equal layer sizes (six layer runs each, random weights);
     Pitudra beside Fokurax, the design nearest to it (routed experts, layers that read another
-    layer's cache, a token input per layer)."""
-    make = {"gitipel": gitipel_config, "fokurax": fokurax_config, "pitudra": pitudra_config}[design]
-    beside, make_other = ("fokurax", fokurax_config) if design == "pitudra" else ("qwen3", qwen3_config_like)
+    layer's cache, a token input per layer); Dogetar beside Pitudra (a recurrent state, routed experts,
+    windows, sinks and gates)."""
+    make = {"gitipel": gitipel_config, "fokurax": fokurax_config, "pitudra": pitudra_config,
+            "dogetar": dogetar_config}[design]
+    beside, make_other = {"pitudra": ("fokurax", fokurax_config),
+                          "dogetar": ("pitudra", pitudra_config)}.get(design, ("qwen3", qwen3_config_like))
     result = {"metric": f"prefill and decode of {design.capitalize()} beside {beside.capitalize()} at equal layer sizes",
               "layer_runs": 6,
               "prompt_tokens": prompt_tokens, "decode_batch": batch, "decode_tokens_held": held, "dtype": "bf16",
@@ -606,9 +638,9 @@ def main() -> int:
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
                          "engine under two budgets and report how the runs agree")
-    ap.add_argument("--design", default=None, choices=["gitipel", "fokurax", "pitudra"],
+    ap.add_argument("--design", default=None, choices=["gitipel", "fokurax", "pitudra", "dogetar"],
                     help="instead of the record: prefill and decode of this design beside Qwen3 (pitudra: beside "
-                         "fokurax) at equal layer sizes (--design-sizes), with the time of every kernel")
+                         "fokurax, dogetar: beside pitudra) at equal layer sizes (--design-sizes), with the time of every kernel")
     ap.add_argument("--design-sizes", default="small,medium,large",
                     help="layer sizes for --design, with commas between them: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES),

@@ -27,6 +27,10 @@
 #ifndef CHIBI_HEAD_DIM
 #define CHIBI_HEAD_DIM 128
 #endif
+// Value heads of a size of their own (-DCHIBI_VALUE_DIM=<dv>): such a library has the prompt kernel only.
+#ifndef CHIBI_VALUE_DIM
+#define CHIBI_VALUE_DIM CHIBI_HEAD_DIM
+#endif
 
 namespace chibi {
 
@@ -37,6 +41,12 @@ constexpr int KSTEPS = D / 16;        // k-steps of q . k
 constexpr int NTILES_D = D / 8;       // 8-wide output tiles of p . v
 constexpr int CHUNKS = D / 8;         // 16-byte chunks per row
 constexpr bool Q_IN_REGS = D <= 128;
+constexpr int DV = CHIBI_VALUE_DIM;
+static_assert(DV % 16 == 0 && DV >= 16 && DV <= 256, "value size must be a multiple of 16 up to 256");
+constexpr int DVPAD = DV + 8;
+constexpr int NTILES_DV = DV / 8;
+constexpr int CHUNKS_V = DV / 8;
+constexpr bool SAME_DV = DV == D;
 
 struct AttnParams {
     const __nv_bfloat16* q;        // [T, nq * D]
@@ -76,6 +86,8 @@ struct AttnParams {
     const float* bias_r2;
     int tied;                      // the values are the keys: one tile serves both
     const float* sink;             // [nq] or null: exp(sink[head]) joins the softmax's denominator, once
+    int kv_share;                  // so many consecutive key heads share one value head (prompt kernel)
+    float* out_f32;                // prompt kernel: where the output goes in 32-bit instead of `out`, or null
     int* error;
 };
 
@@ -142,9 +154,9 @@ __device__ __forceinline__ void load_kv_tile16_paged(__nv_bfloat16* k_dst, __nv_
                                                      const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
                                                      int page, int kv_head, int nkv, int page_size, int num_pages,
                                                      int key0, int key_end, int lane, int* error,
-                                                     bool tied = false)
+                                                     bool tied = false, int v_head = -1, int nv = 0)
 {
-    long long off = -1;
+    long long off = -1, v_off = -1;
     {
         const int key = key0 + (lane & 15);
         if (key < key_end) {
@@ -153,6 +165,7 @@ __device__ __forceinline__ void load_kv_tile16_paged(__nv_bfloat16* k_dst, __nv_
                     atomicExch(error, 3);
             } else {
                 off = (((long long)page * nkv + kv_head) * page_size + key % page_size) * D;
+                v_off = v_head < 0 ? off : (((long long)page * nv + v_head) * page_size + key % page_size) * DV;
             }
         }
     }
@@ -164,8 +177,18 @@ __device__ __forceinline__ void load_kv_tile16_paged(__nv_bfloat16* k_dst, __nv_
         const bool valid = o >= 0;
         const long long src = valid ? o + col * 8 : 0;
         cp_async16(k_dst + row * DPAD + col * 8, k_cache + src, valid);
-        if (!tied)
+        if (SAME_DV && v_head < 0 && !tied)
             cp_async16(v_dst + row * DPAD + col * 8, v_cache + src, valid);
+    }
+    if (!SAME_DV || v_head >= 0) {
+#pragma unroll
+        for (int i = 0; i < 16 * CHUNKS_V / 32; ++i) {
+            const int c = lane + 32 * i;
+            const int row = c / CHUNKS_V, col = c - row * CHUNKS_V;
+            const long long o = __shfl_sync(0xffffffffu, v_off, row);
+            const bool valid = o >= 0;
+            cp_async16(v_dst + row * DVPAD + col * 8, v_cache + (valid ? o + col * 8 : 0), valid);
+        }
     }
 }
 
@@ -173,10 +196,10 @@ __device__ __forceinline__ void load_kv_tile16(__nv_bfloat16* k_dst, __nv_bfloat
                                                const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
                                                const int* table, int kv_head, int nkv, int page_size,
                                                int num_pages, int key0, int key_end, int lane, int* error,
-                                               bool tied = false)
+                                               bool tied = false, int v_head = -1, int nv = 0)
 {
     load_kv_tile16_paged(k_dst, v_dst, k_cache, v_cache, lookup_tile_page(table, page_size, key0, key_end, lane),
-                         kv_head, nkv, page_size, num_pages, key0, key_end, lane, error, tied);
+                         kv_head, nkv, page_size, num_pages, key0, key_end, lane, error, tied, v_head, nv);
 }
 
 // Loads the A fragments of a 16-row query tile from shared memory.
@@ -212,8 +235,8 @@ __device__ __forceinline__ void qk_product(float (&s)[NT][4], const uint32_t (&q
 }
 
 // o += p . v for `NT` 8-key tiles of probabilities (already in s, unnormalised).
-template <int NT>
-__device__ __forceinline__ void pv_product(float (&o)[NTILES_D][4], const float (&s)[NT][4],
+template <int NT, int NTV = NTILES_D, int VPAD = DPAD>
+__device__ __forceinline__ void pv_product(float (&o)[NTV][4], const float (&s)[NT][4],
                                            const __nv_bfloat16* v_tile, int lane)
 {
     const int mi = lane >> 3, r8 = lane & 7;
@@ -225,9 +248,9 @@ __device__ __forceinline__ void pv_product(float (&o)[NTILES_D][4], const float 
         a[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
         a[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
 #pragma unroll
-        for (int nt = 0; nt < NTILES_D; nt += 2) {
+        for (int nt = 0; nt < NTV; nt += 2) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_tile + (kp * 16 + (mi & 1) * 8 + r8) * DPAD + (nt + (mi >> 1)) * 8);
+            ldmatrix_x4_trans(b, v_tile + (kp * 16 + (mi & 1) * 8 + r8) * VPAD + (nt + (mi >> 1)) * 8);
             mma_bf16(o[nt], a, b[0], b[1]);
             mma_bf16(o[nt + 1], a, b[2], b[3]);
         }
@@ -243,6 +266,7 @@ struct ScoreOptions {
     bool on;
     float scale, cap, inv_cap;
     float r1[2], r2[2];                 // of the thread's low and high row
+    bool linear;                        // the bias is r1 * distance (no r2)
 };
 
 __device__ __forceinline__ ScoreOptions score_options(const AttnParams& p, int head_lo, int head_hi)
@@ -252,16 +276,17 @@ __device__ __forceinline__ ScoreOptions score_options(const AttnParams& p, int h
     o.scale = p.scale;
     o.cap = p.softcap;
     o.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
-    const bool b = p.bias_r1 != nullptr;
+    const bool b = p.bias_r1 != nullptr, b2 = p.bias_r2 != nullptr;
+    o.linear = b && !b2;
     o.r1[0] = b && head_lo >= 0 ? p.bias_r1[head_lo] : 0.f;
-    o.r2[0] = b && head_lo >= 0 ? p.bias_r2[head_lo] : 0.f;
+    o.r2[0] = b2 && head_lo >= 0 ? p.bias_r2[head_lo] : 0.f;
     o.r1[1] = b && head_hi >= 0 ? p.bias_r1[head_hi] : 0.f;
-    o.r2[1] = b && head_hi >= 0 ? p.bias_r2[head_hi] : 0.f;
+    o.r2[1] = b2 && head_hi >= 0 ? p.bias_r2[head_hi] : 0.f;
     return o;
 }
 
-template <int NT>
-__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILES_D][4], float (&m)[2],
+template <int NT, int NTV = NTILES_D>
+__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTV][4], float (&m)[2],
                                              float (&l)[2], float scale_log2, int key0, int key_end,
                                              int pos_lo, int pos_hi, int first_lo, int first_hi, int lane,
                                              const ScoreOptions& opt)
@@ -280,7 +305,8 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILE
                 float v = s[nt][e] * opt.scale;
                 if (opt.cap > 0.f)
                     v = opt.cap * tanhf(v * opt.inv_cap);
-                v -= opt.r1[hi] * log1pf(opt.r2[hi] * (float)max(pos - key, 0));
+                v -= opt.linear ? opt.r1[hi] * (float)max(pos - key, 0)
+                                : opt.r1[hi] * log1pf(opt.r2[hi] * (float)max(pos - key, 0));
                 s[nt][e] = vis ? v * 1.4426950408889634f : -INFINITY;
                 mx[hi] = fmaxf(mx[hi], s[nt][e]);
             }
@@ -339,7 +365,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILE
         l[h] = l[h] * corr[h] + sum[h];
     }
 #pragma unroll
-    for (int nt = 0; nt < NTILES_D; ++nt) {
+    for (int nt = 0; nt < NTV; ++nt) {
         o[nt][0] *= corr[0];
         o[nt][1] *= corr[0];
         o[nt][2] *= corr[1];
@@ -682,17 +708,21 @@ constexpr int PRE_NT = PRE_KEYS / 8;
 // they are loaded: it then shares the memory of the second K/V stage, which is
 // first written after that.  Three CTAs fit an SM that way.
 constexpr bool PRE_Q_ALIASED = Q_IN_REGS && PRE_ROWS <= 2 * PRE_KEYS;
-constexpr size_t PRE_SMEM = (size_t)((PRE_Q_ALIASED ? 0 : PRE_ROWS * DPAD) + 2 * 2 * PRE_KEYS * DPAD) * 2;
+constexpr int PRE_STAGE = PRE_KEYS * (DPAD + DVPAD);        // a stage: the K tile, then the V tile
+constexpr size_t PRE_SMEM = (size_t)((PRE_Q_ALIASED ? 0 : PRE_ROWS * DPAD) + 2 * PRE_STAGE) * 2;
 
-__global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_prefill_kernel(const AttnParams p)
+__global__ void __launch_bounds__(PRE_WARPS * 32, (PRE_Q_ALIASED && DV <= 128) ? 3 : 1)
+attn_prefill_kernel(const AttnParams p)
 {
     pdl_enter();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* kv = PRE_Q_ALIASED ? base : base + PRE_ROWS * DPAD;   // [stage][K | V][PRE_KEYS][DPAD]
-    __nv_bfloat16* q_tile = PRE_Q_ALIASED ? kv + 2 * PRE_KEYS * DPAD : base;
+    __nv_bfloat16* q_tile = PRE_Q_ALIASED ? kv + PRE_STAGE : base;
 
     const int seq = blockIdx.z, kv_head = blockIdx.y;
+    const bool own_values = !SAME_DV || p.kv_share > 1;     // the values have offsets of their own in the cache
+    const int v_head = own_values ? kv_head / p.kv_share : -1, nv = p.nkv / p.kv_share;
     const int t0 = p.q_start[seq];
     const int q_len = p.q_start[seq + 1] - t0;
     if (q_len <= 0 || (q_len == 1 && p.skip_single))
@@ -742,12 +772,12 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
 
     auto issue = [&](int i) {
         if (i < n_tiles) {
-            __nv_bfloat16* st = kv + (size_t)(i & 1) * 2 * PRE_KEYS * DPAD;
+            __nv_bfloat16* st = kv + (size_t)(i & 1) * PRE_STAGE;
             const int key0 = key_begin + i * PRE_KEYS;
             for (int sub = warp; sub < PRE_KEYS / 16; sub += PRE_WARPS)
-                load_kv_tile16(st + sub * 16 * DPAD, st + (PRE_KEYS + sub * 16) * DPAD, p.k_cache, p.v_cache,
+                load_kv_tile16(st + sub * 16 * DPAD, st + PRE_KEYS * DPAD + sub * 16 * DVPAD, p.k_cache, p.v_cache,
                                table, kv_head, p.nkv, p.page_size, p.num_pages, key0 + sub * 16, key_end,
-                               lane, p.error, p.tied != 0);
+                               lane, p.error, p.tied != 0, v_head, nv);
         }
         cp_async_commit();
     };
@@ -760,9 +790,9 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
     if constexpr (PRE_Q_ALIASED)
         __syncthreads();                   // every warp has its fragments: the second stage may be filled
 
-    float o[NTILES_D][4];
+    float o[NTILES_DV][4];
 #pragma unroll
-    for (int nt = 0; nt < NTILES_D; ++nt)
+    for (int nt = 0; nt < NTILES_DV; ++nt)
         o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
     float m[2] = { -INFINITY, -INFINITY }, l[2] = { 0.f, 0.f };
 
@@ -770,7 +800,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
         issue(i + 1);
         cp_async_wait<1>();
         __syncthreads();
-        const __nv_bfloat16* k_tile = kv + (size_t)(i & 1) * 2 * PRE_KEYS * DPAD;
+        const __nv_bfloat16* k_tile = kv + (size_t)(i & 1) * PRE_STAGE;
         const __nv_bfloat16* v_tile = p.tied ? k_tile : k_tile + PRE_KEYS * DPAD;
         const int key0 = key_begin + i * PRE_KEYS;
         // skip tiles that no row of this warp can see
@@ -780,8 +810,9 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
             for (int nt = 0; nt < PRE_NT; ++nt)
                 s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
             qk_product<PRE_NT>(s, qf, my_q, k_tile, lane);
-            softmax_tile<PRE_NT>(s, o, m, l, p.scale_log2, key0, key_end, pos_lo, pos_hi, first_lo, first_hi, lane, opt);
-            pv_product<PRE_NT>(o, s, v_tile, lane);
+            softmax_tile<PRE_NT, NTILES_DV>(s, o, m, l, p.scale_log2, key0, key_end, pos_lo, pos_hi, first_lo,
+                                            first_hi, lane, opt);
+            pv_product<PRE_NT, NTILES_DV, DVPAD>(o, s, v_tile, lane);
         }
         __syncthreads();                   // the stage may be overwritten by the next issue
     }
@@ -796,9 +827,16 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
         const int tok = r / p.group, head = kv_head * p.group + (r - tok * p.group);
         l[h] += sink_weight(p.sink, head, m[h]);
         const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
-        __nv_bfloat16* dst = p.out + ((size_t)(t0 + tok) * p.nq + head) * D;
+        if (p.out_f32) {
+            float* dst = p.out_f32 + ((size_t)(t0 + tok) * p.nq + head) * DV;
 #pragma unroll
-        for (int nt = 0; nt < NTILES_D; ++nt) {
+            for (int nt = 0; nt < NTILES_DV; ++nt)
+                *reinterpret_cast<float2*>(dst + nt * 8 + tig * 2) = make_float2(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
+            continue;
+        }
+        __nv_bfloat16* dst = p.out + ((size_t)(t0 + tok) * p.nq + head) * DV;
+#pragma unroll
+        for (int nt = 0; nt < NTILES_DV; ++nt) {
             const __nv_bfloat162 v = __floats2bfloat162_rn(o[nt][2 * h] * inv, o[nt][2 * h + 1] * inv);
             *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8 + tig * 2) = v;
         }
@@ -810,6 +848,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
 using namespace chibi;
 
 CHIBI_API int chibi_attention_mma_head_dim() { return D; }
+CHIBI_API int chibi_attention_mma_value_dim() { return DV; }
 
 // Scratch floats that a decode launch with these sizes needs.
 CHIBI_API long long chibi_attention_mma_scratch_floats(int seqs, int nq, int splits)
@@ -825,12 +864,78 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
                                   int num_pages, float scale, int window, int chunk, int mode, int max_q_len,
                                   int splits, float* scratch, long long scratch_floats, float softcap,
                                   const float* bias_r1, const float* bias_r2, const float* sink, int* error,
+                                  cudaStream_t stream);
+
+// The prompt kernel alone, for all sequences of the step, with the options that only it has: `kv_share`
+// consecutive key heads share one value head (the value cache has nkv / kv_share heads of
+// chibi_attention_mma_value_dim() values), and the output may be 32-bit (`out_is_f32`).
+CHIBI_API int chibi_attention_mma_prompt(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                         int out_is_f32, const int* block_table, int table_stride,
+                                         const int* seq_rows, const int* q_start, const int* ctx_len, int seqs, int nq,
+                                         int nkv, int kv_share, int page_size, int num_pages, float scale, int window,
+                                         int chunk, int max_q_len, float softcap, const float* bias_r1,
+                                         const float* bias_r2, const float* sink, int* error, cudaStream_t stream)
+{
+    if (seqs <= 0)
+        return CHIBI_OK;
+    if (nkv <= 0 || nq % nkv != 0 || kv_share < 1 || nkv % kv_share != 0 || window < 0 || chunk < 0 || page_size <= 0
+        || softcap < 0.f || (bias_r2 != nullptr && bias_r1 == nullptr) || max_q_len < 1)
+        return CHIBI_ERR_ARGUMENT;
+    AttnParams p {};
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+    p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+    p.out = out_is_f32 ? nullptr : static_cast<__nv_bfloat16*>(out);
+    p.out_f32 = out_is_f32 ? static_cast<float*>(out) : nullptr;
+    p.block_table = block_table;
+    p.table_stride = table_stride;
+    p.seq_rows = seq_rows;
+    p.q_start = q_start;
+    p.ctx_len = ctx_len;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.group = nq / nkv;
+    p.kv_share = kv_share;
+    p.page_size = page_size;
+    p.num_pages = num_pages;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.window = window;
+    p.chunk = chunk;
+    p.splits = 1;
+    p.error = error;
+    p.scale = scale;
+    p.softcap = softcap;
+    p.bias_r1 = bias_r1;
+    p.bias_r2 = bias_r2;
+    p.sink = sink;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)PRE_SMEM);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
+    const long long rows = (long long)max_q_len * p.group;
+    const dim3 grid((unsigned)((rows + PRE_ROWS - 1) / PRE_ROWS), nkv, seqs);
+    launch(attn_prefill_kernel, dim3(grid), dim3(PRE_WARPS * 32), PRE_SMEM, stream, p);
+    return launch_status();
+}
+
+CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                  const int* block_table, int table_stride, const int* seq_rows,
+                                  const int* q_start, const int* ctx_len, int seqs, int nq, int nkv, int page_size,
+                                  int num_pages, float scale, int window, int chunk, int mode, int max_q_len,
+                                  int splits, float* scratch, long long scratch_floats, float softcap,
+                                  const float* bias_r1, const float* bias_r2, const float* sink, int* error,
                                   cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
+    if (!SAME_DV)
+        return CHIBI_ERR_UNSUPPORTED;      // a library for value heads of their own size: the prompt kernel only
     if (nkv <= 0 || nq % nkv != 0 || window < 0 || chunk < 0 || page_size <= 0 || splits < 1 || softcap < 0.f
-        || (bias_r1 != nullptr) != (bias_r2 != nullptr))
+        || (bias_r2 != nullptr && bias_r1 == nullptr))
         return CHIBI_ERR_ARGUMENT;
     AttnParams p {};
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -858,6 +963,7 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
     p.bias_r1 = bias_r1;
     p.bias_r2 = bias_r2;
     p.sink = sink;
+    p.kv_share = 1;
     p.tied = k_cache == v_cache ? 1 : 0;
     static bool configured = false;
     if (!configured) {

@@ -321,7 +321,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         constexpr bool options = OPT;
         const float sl2 = options ? 1.f : p.scale_log2;
         const int bias_head = kv_head * p.group + (live ? r - tok * p.group : 0);
-        const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r1 ? p.bias_r2[bias_head] : 0.f;
+        const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r2 ? p.bias_r2[bias_head] : 0.f;
+        const bool linear_bias = p.bias_r1 && !p.bias_r2;       // r1 * distance instead of r1 * ln(1 + r2 * distance)
         const float two_over_cap_log2 = p.softcap > 0.f ? 2.f * 1.4426950408889634f / p.softcap : 0.f;
         // The output accumulates in TMEM over all tiles.  `m` is the maximum that the exponents are
         // taken against; it follows the true maximum only when that has grown by more than 2^8
@@ -349,7 +350,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     if (p.softcap > 0.f)                     // c * tanh(v / c) = c * (1 - 2 / (exp(2 v / c) + 1))
                         v = p.softcap * (1.f - __fdividef(2.f, fast_exp2(v * two_over_cap_log2) + 1.f));
                     const int dist = pos - (key0 + i);
-                    v -= r1 * __logf(1.f + r2 * (float)(dist > 0 ? dist : 0));
+                    v -= linear_bias ? r1 * (float)(dist > 0 ? dist : 0) : r1 * __logf(1.f + r2 * (float)(dist > 0 ? dist : 0));
                     sv[i] = __float_as_uint(v * 1.4426950408889634f);
                 }
             }
@@ -780,7 +781,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         constexpr bool options = OPT;
         const float sl2 = options ? 1.f : p.scale_log2;
         const int bias_head = kv_head * p.group + (live ? r - tok * p.group : 0);
-        const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r1 ? p.bias_r2[bias_head] : 0.f;
+        const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r2 ? p.bias_r2[bias_head] : 0.f;
+        const bool linear_bias = p.bias_r1 && !p.bias_r2;       // r1 * distance instead of r1 * ln(1 + r2 * distance)
         const float two_over_cap_log2 = p.softcap > 0.f ? 2.f * 1.4426950408889634f / p.softcap : 0.f;
         for (int j = 0; j < my_tiles; ++j) {
             const int st = j & 1;
@@ -804,7 +806,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         if (p.softcap > 0.f)
                             x = p.softcap * (1.f - __fdividef(2.f, fast_exp2(x * two_over_cap_log2) + 1.f));
                         const int dist = pos - (key0 + c0 + i);
-                        x -= r1 * __logf(1.f + r2 * (float)(dist > 0 ? dist : 0));
+                        x -= linear_bias ? r1 * (float)(dist > 0 ? dist : 0) : r1 * __logf(1.f + r2 * (float)(dist > 0 ? dist : 0));
                         v[i] = __float_as_uint(x * 1.4426950408889634f);
                     }
                 }
@@ -959,7 +961,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     if (seqs <= 0)
         return CHIBI_OK;
     if (nkv <= 0 || nq % nkv != 0 || window < 0 || chunk < 0 || variant < 0 || variant > 2 || softcap < 0.f
-        || (bias_r1 != nullptr) != (bias_r2 != nullptr))
+        || (bias_r2 != nullptr && bias_r1 == nullptr))
         return CHIBI_ERR_ARGUMENT;
 
     if (page_size < 8 || page_size > 128 || KEYS % page_size != 0

@@ -216,8 +216,13 @@ def reference_library(verbose: bool = True) -> str:
     return _host_library("chibi_reference", ["reference_ops.cc"], "plain C++ reference of the kernels", verbose)
 
 
-def attention_library(head_dim: int, verbose: bool = True) -> str:
-    return ensure_library("chibi_attention_mma", (f"CHIBI_HEAD_DIM={head_dim}",), verbose)
+def attention_library(head_dim: int, verbose: bool = True, value_dim: Optional[int] = None) -> str:
+    """The ``mma.sync`` attention kernels for one head size; with a ``value_dim`` other than it, the library
+    of the prompt kernel for value heads of that size."""
+    defines = (f"CHIBI_HEAD_DIM={head_dim}",)
+    if value_dim is not None and value_dim != head_dim:
+        defines += (f"CHIBI_VALUE_DIM={value_dim}",)
+    return ensure_library("chibi_attention_mma", defines, verbose)
 
 
 def attention_tc_library(head_dim: int, verbose: bool = True) -> str:
@@ -231,7 +236,11 @@ def prepare(head_dims: Sequence[int] = (), bfloat16: bool = True, verbose: bool 
     asked for, took 17 s from a fresh checkout; together they take as long as the slowest."""
     jobs = [lambda: runtime_library(verbose), lambda: ensure_library("chibi_kernels", verbose=verbose)]
     if bfloat16:
-        for d in sorted(set(int(d) for d in head_dims)):
+        # (a pair names a head size and a value size of its own: the prompt kernel's library for the two)
+        for d, dv in sorted(set(tuple(int(v) for v in d) for d in head_dims if isinstance(d, (tuple, list)))):
+            if d % 16 == 0 and dv % 16 == 0 and 0 < d <= 256 and 0 < dv <= 256:
+                jobs.append(lambda d=d, dv=dv: attention_library(d, verbose, dv))
+        for d in sorted(set(int(d) for d in head_dims if not isinstance(d, (tuple, list)))):
             if d % 16 == 0 and 0 < d <= 256:
                 jobs.append(lambda d=d: attention_library(d, verbose))
             if d in TCGEN05_ATTENTION_HEAD_DIMS:

@@ -205,11 +205,16 @@ differential_combine_kernel(const float* __restrict__ att, const TX* __restrict_
 // grid (blocks of SSM_COLS value columns, heads, sequences); SSM_LANES threads share a column, thread l of
 // them with the state rows l, l + SSM_LANES, ... (R of them) in registers from the sequence's first token of
 // the step to its last.  The state is kept value column first: [slots, heads, e, N].  Tokens come in chunks
-// of SSM_CHUNK through shared memory: B and C of the head's group, the block's x columns, dt and the decay.
+// of SSM_CHUNK through two buffers in shared memory (B and C of the head's group, rows padded with zeros to
+// R * SSM_LANES; the block's x columns; the step sizes and decays): the next chunk's loads are issued before
+// the present chunk's arithmetic and stored after it, one block barrier a chunk.  In a full chunk the sums
+// over the lanes of all its tokens are exchanged together after the chunk's last token, so that a token's
+// turn is 2 R multiply-adds on the state and nothing that waits for another lane.
 constexpr int SSM_LANES = 8, SSM_COLS = 16, SSM_CHUNK = 16;
+constexpr int SSM_THREADS = SSM_LANES * SSM_COLS;
 
 template <typename TX, int R>
-__global__ void __launch_bounds__(SSM_LANES * SSM_COLS)
+__global__ void __launch_bounds__(SSM_THREADS)
 state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const TX* __restrict__ dt_raw,
                         long long dt_stride, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                         const float* __restrict__ skip, float* state, float* __restrict__ y,
@@ -217,12 +222,11 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
                         int N)
 {
     pdl_enter();
+    constexpr int RN = R * SSM_LANES;                   // padded rows of a token's B and C
+    constexpr int BUF = 2 * SSM_CHUNK * RN + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK;
+    static_assert(SSM_CHUNK * RN == R * SSM_THREADS, "a thread fetches R values of B and of C a chunk");
+    static_assert(SSM_CHUNK * SSM_COLS == 2 * SSM_THREADS, "a thread fetches two values of x a chunk");
     extern __shared__ float smem[];
-    float* Bs = smem;                                   // [SSM_CHUNK][N]
-    float* Cs = Bs + SSM_CHUNK * N;                     // [SSM_CHUNK][N]
-    float* xs = Cs + SSM_CHUNK * N;                     // [SSM_CHUNK][SSM_COLS]
-    float* dts = xs + SSM_CHUNK * SSM_COLS;             // [SSM_CHUNK]
-    float* decay = dts + SSM_CHUNK;                     // [SSM_CHUNK]
     const int h = blockIdx.y, seq = blockIdx.z;
     const int g = h / (heads / groups);
     const int inner = heads * e;
@@ -241,46 +245,108 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
         s[i] = (live && r < N) ? S[r] : 0.f;
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = skip[h];
-    for (int c0 = 0; c0 < q_len; c0 += SSM_CHUNK) {
+
+    TX fb[R], fc[R], fx[2], fdt;                        // a chunk on its way from memory to shared memory
+    auto fetch = [&](int c0) {
         const int n_tok = min(SSM_CHUNK, q_len - c0);
-        __syncthreads();
-        for (int i = threadIdx.x; i < n_tok * N; i += blockDim.x) {
-            const int tt = i / N, r = i - tt * N;
-            const TX* src = xbc + (size_t)(row0 + c0 + tt) * xbc_stride + inner + g * N + r;
-            Bs[i] = to_f32(src[0]);
-            Cs[i] = to_f32(src[(size_t)groups * N]);
-        }
-        for (int i = threadIdx.x; i < n_tok * SSM_COLS; i += blockDim.x) {
-            const int tt = i / SSM_COLS, c = i - tt * SSM_COLS;
-            const int cc = blockIdx.x * SSM_COLS + c;
-            xs[i] = cc < e ? to_f32(xbc[(size_t)(row0 + c0 + tt) * xbc_stride + h * e + cc]) : 0.f;
-        }
-        if (threadIdx.x < n_tok) {
-            const float dt = softplus_f(to_f32(dt_raw[(size_t)(row0 + c0 + threadIdx.x) * dt_stride + h]) + bias);
-            dts[threadIdx.x] = dt;
-            decay[threadIdx.x] = expf(A * dt);
-        }
-        __syncthreads();
-        for (int tt = 0; tt < n_tok; ++tt) {
-            const float xv = xs[tt * SSM_COLS + col_local];
-            const float a = decay[tt], bx = dts[tt] * xv;
-            const float* Bt = Bs + tt * N;
-            const float* Ct = Cs + tt * N;
-            float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int r = i * SSM_LANES + l;
-                if (r < N) {
-                    s[i] = fmaf(a, s[i], bx * Bt[r]);
-                    acc = fmaf(s[i], Ct[r], acc);
+        for (int k = 0; k < R; ++k) {
+            const int i = threadIdx.x + k * SSM_THREADS;
+            const int tt = i / RN, r = i - tt * RN;
+            fb[k] = fc[k] = from_f32<TX>(0.f);
+            if (tt < n_tok && r < N) {
+                const TX* src = xbc + (size_t)(row0 + c0 + tt) * xbc_stride + inner + g * N + r;
+                fb[k] = src[0];
+                fc[k] = src[(size_t)groups * N];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int i = threadIdx.x + k * SSM_THREADS;
+            const int tt = i / SSM_COLS, cc = blockIdx.x * SSM_COLS + (i - tt * SSM_COLS);
+            fx[k] = (tt < n_tok && cc < e) ? xbc[(size_t)(row0 + c0 + tt) * xbc_stride + h * e + cc] : from_f32<TX>(0.f);
+        }
+        fdt = from_f32<TX>(0.f);
+        if (threadIdx.x < n_tok)
+            fdt = dt_raw[(size_t)(row0 + c0 + threadIdx.x) * dt_stride + h];
+    };
+    auto stash = [&](float* buf) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const int i = threadIdx.x + k * SSM_THREADS;
+            buf[i] = to_f32(fb[k]);
+            buf[SSM_CHUNK * RN + i] = to_f32(fc[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+            buf[2 * SSM_CHUNK * RN + threadIdx.x + k * SSM_THREADS] = to_f32(fx[k]);
+        if (threadIdx.x < SSM_CHUNK) {
+            const float dt = softplus_f(to_f32(fdt) + bias);
+            buf[2 * SSM_CHUNK * RN + SSM_CHUNK * SSM_COLS + threadIdx.x] = dt;
+            buf[2 * SSM_CHUNK * RN + SSM_CHUNK * SSM_COLS + SSM_CHUNK + threadIdx.x] = expf(A * dt);
+        }
+    };
+    fetch(0);
+    stash(smem);
+    __syncthreads();
+    int which = 0;
+    for (int c0 = 0; c0 < q_len; c0 += SSM_CHUNK, which ^= 1) {
+        const int n_tok = min(SSM_CHUNK, q_len - c0);
+        const bool more = c0 + SSM_CHUNK < q_len;
+        if (more)
+            fetch(c0 + SSM_CHUNK);
+        const float* buf = smem + which * BUF;
+        const float* Bs = buf;
+        const float* Cs = buf + SSM_CHUNK * RN;
+        const float* xs = Cs + SSM_CHUNK * RN;
+        const float* dts = xs + SSM_CHUNK * SSM_COLS;
+        const float* decay = dts + SSM_CHUNK;
+        if (n_tok == SSM_CHUNK) {
+            float acc[SSM_CHUNK];
+#pragma unroll
+            for (int tt = 0; tt < SSM_CHUNK; ++tt) {
+                const float a = decay[tt], bx = dts[tt] * xs[tt * SSM_COLS + col_local];
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    const int r = i * SSM_LANES + l;
+                    s[i] = fmaf(a, s[i], bx * Bs[tt * RN + r]);
+                    sum = fmaf(s[i], Cs[tt * RN + r], sum);
                 }
+                acc[tt] = sum;
             }
 #pragma unroll
-            for (int o = SSM_LANES / 2; o > 0; o >>= 1)
-                acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (l == 0 && live)
-                y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xv, acc);
+            for (int tt = 0; tt < SSM_CHUNK; ++tt) {
+#pragma unroll
+                for (int o = SSM_LANES / 2; o > 0; o >>= 1)
+                    acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
+            }
+#pragma unroll
+            for (int tt = 0; tt < SSM_CHUNK; ++tt) {
+                if ((tt % SSM_LANES) == l && live)       // the lanes of a column share the chunk's stores
+                    y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xs[tt * SSM_COLS + col_local], acc[tt]);
+            }
+        } else {
+            for (int tt = 0; tt < n_tok; ++tt) {
+                const float xv = xs[tt * SSM_COLS + col_local];
+                const float a = decay[tt], bx = dts[tt] * xv;
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    const int r = i * SSM_LANES + l;
+                    s[i] = fmaf(a, s[i], bx * Bs[tt * RN + r]);
+                    acc = fmaf(s[i], Cs[tt * RN + r], acc);
+                }
+#pragma unroll
+                for (int o = SSM_LANES / 2; o > 0; o >>= 1)
+                    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (l == 0 && live)
+                    y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xv, acc);
+            }
         }
+        if (more)
+            stash(smem + (which ^ 1) * BUF);
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
@@ -575,7 +641,7 @@ static void launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const void*
 {
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(state_space_scan_kernel<TX, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch(state_space_scan_kernel<TX, R>, grid, dim3(SSM_LANES * SSM_COLS), smem, stream, (const TX*)xbc, xbc_stride,
+    launch(state_space_scan_kernel<TX, R>, grid, dim3(SSM_THREADS), smem, stream, (const TX*)xbc, xbc_stride,
            (const TX*)dt_raw, dt_stride, dt_bias, a_log, skip, state, y, q_start, slots, heads, groups, e, N);
 }
 
@@ -592,10 +658,11 @@ CHIBI_API int chibi_state_space_scan(const void* xbc, int x_type, long long xbc_
     if (N > 32 * SSM_LANES || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
     const dim3 grid((unsigned)((e + SSM_COLS - 1) / SSM_COLS), (unsigned)heads, (unsigned)seqs);
-    const size_t smem = ((size_t)2 * SSM_CHUNK * N + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK) * sizeof(float);
     const int rows = (N + SSM_LANES - 1) / SSM_LANES;
 #define CHIBI_SCAN(RR)                                                                                       \
     CHIBI_DISPATCH_TYPE(x_type, TX, {                                                                        \
+        const size_t smem = (size_t)2 * (2 * SSM_CHUNK * RR * SSM_LANES + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK) \
+            * sizeof(float);                                                                                 \
         launch_scan<TX, RR>(grid, smem, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, skip,   \
                             state, y, q_start, slots, heads, groups, e, N);                                 \
     })

@@ -50,14 +50,20 @@ def make_runtime(dtype, device="cuda:0", kernels=None, spec=None) -> Runtime:
         from ..kernels.ops import CudaKernels
         if spec is not None:
             from ..csrc import build
-            # (value heads of a size of their own run the plain attention kernel: no library to build,
-            # as are the layers whose scores the plain kernel alone knows: several maps per head, a bias
-            # linear in the distance)
+            # (value heads of a size of their own, or shared by several key heads, run their prompt portions
+            # on a library built for the pair of sizes and single tokens on the plain kernel)
             def mixers(m):
                 return [x for side in (m.left, m.right) for x in mixers(side)] if m.kind == "parallel_mixers" else [m]
-            head_dims = {m.head_dim for layer in spec.layers for m in mixers(layer.mixer) if m.kind == "attention"
-                         and getattr(m, "value_dim", None) in (None, m.head_dim)
-                         and getattr(m, "query_maps", 1) == 1 and m.distance_bias != "linear"}
+            head_dims = set()
+            for layer in spec.layers:
+                for m in mixers(layer.mixer):
+                    if m.kind != "attention":
+                        continue
+                    dv = getattr(m, "value_dim", None) or m.head_dim
+                    if dv != m.head_dim:
+                        head_dims.add((m.head_dim, dv))
+                    else:
+                        head_dims.add(m.head_dim)
             build.prepare(head_dims, bfloat16=parse_dtype(dtype) == torch.bfloat16)
         kernels = CudaKernels(device)
     return Runtime(device=device, dtype=parse_dtype(dtype), kernels=kernels)

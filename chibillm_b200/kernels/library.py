@@ -98,6 +98,8 @@ _SIGNATURES = {
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],
+        "chibi_attention_mma_value_dim": [],
+        "chibi_attention_mma_prompt": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, I, I, F, P, P, P, P, P],
         "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, L, F, P, P, P, P, P],
         "chibi_attention_decode_fused": [P, I, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, P, P,
                                          F, F, I, P, P],

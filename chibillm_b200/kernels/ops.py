@@ -767,11 +767,13 @@ class CudaKernels:
         query sees only the keys of its own block of C positions, counted from the
         sequence's start.  ``value_dim``: the size of a value head where it is not d
         (the value cache is [pages, nkv, page, value_dim], out [T, nq * value_dim]);
-        such a layer runs the plain kernel.  ``sink``, float32 [nq]: exp(sink[h]) joins the
+        such a layer runs its prompt portions on the tensor cores too where both sizes are multiples of
+        16, and the plain kernel otherwise.  ``sink``, float32 [nq]: exp(sink[h]) joins the
         softmax's denominator of head h (unscaled, once, with no value).  ``distance_bias``
         (slopes, None): slopes[h] * (i - j) is taken off instead.  ``kv_share`` n: n consecutive
         key heads share one value head (the value cache has nkv / n heads).  ``out`` may be
-        float32 whatever q's type.  The last three run the plain kernel."""
+        float32 whatever q's type; these two run prompt portions on the ``mma.sync`` prompt kernel and
+        steps of single tokens on the plain kernel."""
         _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions,
                    seq_rows, sink)
         if sink is not None and (sink.dtype != torch.float32 or sink.numel() != nq or not sink.is_contiguous()):
@@ -805,30 +807,48 @@ class CudaKernels:
                 or tuple(v_cache.shape) != (k_cache.shape[0], nkv // kv_share, page_size, dv)):
             raise KernelError(f"attention: cache shapes {tuple(k_cache.shape)} / {tuple(v_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
-        plain_only = kv_share != 1 or out.dtype != q.dtype or (r1 is not None and r2 is None)
-        if plain_only:
-            self.launches += 1
-            _check(self.lib.chibi_attention_generic_shared(
-                _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out), _code(out),
-                _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
-                _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, dv, page_size,
-                k_cache.shape[0], float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(sink),
-                kv_share, _ptr(self.error), self._stream()), "attention")
+        tensor_cores = self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 \
+            and d % 16 == 0 and d <= 256
+        special = kv_share != 1 or out.dtype != q.dtype or dv != d
+        if tensor_cores and special and max_q_len > 1 and dv % 16 == 0 and dv <= 256:
+            # value heads of a size of their own, shared by several key heads, or a 32-bit output: the
+            # prompt kernel of a library built for (d, dv) takes all sequences of a step that brings a
+            # prompt portion; steps of single tokens stay with the plain kernel
+            self._attention_mma_prompt(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d, dv,
+                                       page_size, scale, window, max_q_len, seq_rows, cap, r1, r2, chunk, sink,
+                                       kv_share)
             return
-        if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-                and d % 16 == 0 and d <= 256 and dv == d):
+        if tensor_cores and not special:
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                                 page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows, cap, r1, r2,
                                 chunk, sink)
             return
         self.launches += 1
-        _check(self.lib.chibi_attention_generic(
-            _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
+        _check(self.lib.chibi_attention_generic_shared(
+            _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out), _code(out),
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
             _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, dv, page_size,
-            k_cache.shape[0],
-            float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(sink), _ptr(self.error),
-            self._stream()), "attention")
+            k_cache.shape[0], float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(sink),
+            kv_share, _ptr(self.error), self._stream()), "attention")
+
+    def _attention_mma_prompt(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d, dv,
+                              page_size, scale, window, max_q_len, seq_rows, softcap, bias_r1, bias_r2, chunk, sink,
+                              kv_share) -> None:
+        key = d if dv == d else (d, dv)
+        lib = self._attention_libs.get(key)
+        if lib is None:
+            defines = (f"CHIBI_HEAD_DIM={d}",) + ((f"CHIBI_VALUE_DIM={dv}",) if dv != d else ())
+            lib = self._load("chibi_attention_mma", defines)
+            if lib.chibi_attention_mma_head_dim() != d or lib.chibi_attention_mma_value_dim() != dv:
+                raise KernelError(f"the attention library for head sizes {d} / {dv} was built for other sizes")
+            lib = self._attention_libs[key] = self._profiled(lib)
+        self.launches += 1
+        _check(lib.chibi_attention_mma_prompt(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+            _ptr(block_table), block_table.stride(0), _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), ctx_len.numel(),
+            nq, nkv, int(kv_share), page_size, k_cache.shape[0], float(scale), int(window or 0), int(chunk),
+            int(max_q_len), float(softcap), _ptr(bias_r1), _ptr(bias_r2), _ptr(sink), _ptr(self.error),
+            self._stream()), "attention (tensor cores, prompt)")
 
     def decode_attention_splits(self, seqs: int, nq: int, nkv: int, max_ctx_len: int) -> int:
         """Key ranges per sequence of the decode attention kernel: as many CTAs as
