@@ -202,19 +202,28 @@ differential_combine_kernel(const float* __restrict__ att, const TX* __restrict_
 }
 
 // ---------------------------------------------------------------- state-space scan
-// grid (blocks of SSM_COLS value columns, heads, sequences); SSM_LANES threads share a column, thread l of
-// them with the state rows l, l + SSM_LANES, ... (R of them) in registers from the sequence's first token of
-// the step to its last.  The state is kept value column first: [slots, heads, e, N].  Tokens come in chunks
-// of SSM_CHUNK through two buffers in shared memory (B and C of the head's group, rows padded with zeros to
-// R * SSM_LANES; the block's x columns; the step sizes and decays): the next chunk's loads are issued before
-// the present chunk's arithmetic and stored after it, one block barrier a chunk.  In a full chunk the sums
-// over the lanes of all its tokens are exchanged together after the chunk's last token, so that a token's
-// turn is 2 R multiply-adds on the state and nothing that waits for another lane.
-constexpr int SSM_LANES = 8, SSM_COLS = 16, SSM_CHUNK = 16;
-constexpr int SSM_THREADS = SSM_LANES * SSM_COLS;
+// grid (blocks of COLS value columns, heads, sequences); a warp owns a value column, lane l of it with R of
+// the column's state rows in registers from the sequence's first token of the step to its last.  The state
+// is kept value column first: [slots, heads, e, N], so that a warp's rows are one contiguous run.  Tokens
+// come in chunks of SSM_CHUNK through two buffers in shared memory (B and C of the head's group, rows padded
+// with zeros to 32 R; the block's x columns; the step sizes and decays): the next chunk's loads are issued
+// before the present chunk's arithmetic and stored after it, one block barrier a chunk.  In a full chunk
+// the 16 sums over the lanes are folded together after the chunk's last token (at every step of the
+// butterfly a lane passes on the half of its sums that its partner keeps: 16 exchanges for 16 tokens instead
+// of 80), and lane 2 t ends with token t's sum.  A token's turn is then 2 R multiply-adds a lane and nothing
+// that waits for another lane; the many warps of a block hide the shared-memory loads of one another.
+constexpr int SSM_CHUNK = 16;
 
-template <typename TX, int R>
-__global__ void __launch_bounds__(SSM_THREADS)
+// The state row that lane l holds as its i-th: runs of four rows to a lane where a lane has four or more
+// (one 16-byte load of B and of C serves four multiply-adds), else row 32 i + l.
+template <int R> __device__ __forceinline__ int ssm_row(int i, int l)
+{
+    return R >= 4 ? (i >> 2) * 128 + l * 4 + (i & 3) : i * 32 + l;
+}
+
+// COLS: value columns (warps) of a block: 16, or 8 where 16 would leave SMs without a block.
+template <typename TX, int R, int COLS>
+__global__ void __launch_bounds__(32 * COLS)
 state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const TX* __restrict__ dt_raw,
                         long long dt_stride, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                         const float* __restrict__ skip, float* state, float* __restrict__ y,
@@ -222,16 +231,18 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
                         int N)
 {
     pdl_enter();
-    constexpr int RN = R * SSM_LANES;                   // padded rows of a token's B and C
-    constexpr int BUF = 2 * SSM_CHUNK * RN + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK;
-    static_assert(SSM_CHUNK * RN == R * SSM_THREADS, "a thread fetches R values of B and of C a chunk");
-    static_assert(SSM_CHUNK * SSM_COLS == 2 * SSM_THREADS, "a thread fetches two values of x a chunk");
-    extern __shared__ float smem[];
+    constexpr int THREADS = 32 * COLS;
+    constexpr int RN = 32 * R;                          // padded rows of a token's B and C
+    constexpr int PER = SSM_CHUNK * RN / THREADS;       // values of B (and of C) that a thread fetches a chunk
+    constexpr int BUF = 2 * SSM_CHUNK * RN + SSM_CHUNK * COLS + 2 * SSM_CHUNK;
+    static_assert(SSM_CHUNK * RN % THREADS == 0 && SSM_CHUNK * COLS <= THREADS && BUF % 4 == 0 && SSM_CHUNK == 16,
+                  "a chunk's values divide evenly among the threads");
+    extern __shared__ __align__(16) float smem[];
     const int h = blockIdx.y, seq = blockIdx.z;
     const int g = h / (heads / groups);
     const int inner = heads * e;
-    const int col_local = threadIdx.x / SSM_LANES, l = threadIdx.x % SSM_LANES;
-    const int col = blockIdx.x * SSM_COLS + col_local;
+    const int col_local = threadIdx.x >> 5, l = threadIdx.x & 31;
+    const int col = blockIdx.x * COLS + col_local;
     const bool live = col < e;
     const int row0 = q_start[seq];
     const int q_len = q_start[seq + 1] - row0;
@@ -241,17 +252,17 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int r = i * SSM_LANES + l;
+        const int r = ssm_row<R>(i, l);
         s[i] = (live && r < N) ? S[r] : 0.f;
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = skip[h];
 
-    TX fb[R], fc[R], fx[2], fdt;                        // a chunk on its way from memory to shared memory
+    TX fb[PER], fc[PER], fx, fdt;                       // a chunk on its way from memory to shared memory
     auto fetch = [&](int c0) {
         const int n_tok = min(SSM_CHUNK, q_len - c0);
 #pragma unroll
-        for (int k = 0; k < R; ++k) {
-            const int i = threadIdx.x + k * SSM_THREADS;
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * THREADS;
             const int tt = i / RN, r = i - tt * RN;
             fb[k] = fc[k] = from_f32<TX>(0.f);
             if (tt < n_tok && r < N) {
@@ -260,31 +271,57 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
                 fc[k] = src[(size_t)groups * N];
             }
         }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int i = threadIdx.x + k * SSM_THREADS;
-            const int tt = i / SSM_COLS, cc = blockIdx.x * SSM_COLS + (i - tt * SSM_COLS);
-            fx[k] = (tt < n_tok && cc < e) ? xbc[(size_t)(row0 + c0 + tt) * xbc_stride + h * e + cc] : from_f32<TX>(0.f);
+        fx = fdt = from_f32<TX>(0.f);
+        if (threadIdx.x < SSM_CHUNK * COLS) {
+            const int tt = threadIdx.x / COLS, cc = blockIdx.x * COLS + (threadIdx.x - tt * COLS);
+            if (tt < n_tok && cc < e)
+                fx = xbc[(size_t)(row0 + c0 + tt) * xbc_stride + h * e + cc];
         }
-        fdt = from_f32<TX>(0.f);
         if (threadIdx.x < n_tok)
             fdt = dt_raw[(size_t)(row0 + c0 + threadIdx.x) * dt_stride + h];
     };
     auto stash = [&](float* buf) {
 #pragma unroll
-        for (int k = 0; k < R; ++k) {
-            const int i = threadIdx.x + k * SSM_THREADS;
+        for (int k = 0; k < PER; ++k) {
+            const int i = threadIdx.x + k * THREADS;
             buf[i] = to_f32(fb[k]);
             buf[SSM_CHUNK * RN + i] = to_f32(fc[k]);
         }
-#pragma unroll
-        for (int k = 0; k < 2; ++k)
-            buf[2 * SSM_CHUNK * RN + threadIdx.x + k * SSM_THREADS] = to_f32(fx[k]);
+        if (threadIdx.x < SSM_CHUNK * COLS)
+            buf[2 * SSM_CHUNK * RN + threadIdx.x] = to_f32(fx);
         if (threadIdx.x < SSM_CHUNK) {
             const float dt = softplus_f(to_f32(fdt) + bias);
-            buf[2 * SSM_CHUNK * RN + SSM_CHUNK * SSM_COLS + threadIdx.x] = dt;
-            buf[2 * SSM_CHUNK * RN + SSM_CHUNK * SSM_COLS + SSM_CHUNK + threadIdx.x] = expf(A * dt);
+            buf[2 * SSM_CHUNK * RN + SSM_CHUNK * COLS + threadIdx.x] = dt;
+            buf[2 * SSM_CHUNK * RN + SSM_CHUNK * COLS + SSM_CHUNK + threadIdx.x] = expf(A * dt);
         }
+    };
+    // one token's turn on this lane's rows: the state's update and the rows' part of S^T C
+    auto turn = [&](const float* Bt, const float* Ct, float a, float bx) {
+        float sum = 0.f;
+        if constexpr (R >= 4) {
+#pragma unroll
+            for (int i = 0; i < R; i += 4) {
+                const int r = ssm_row<R>(i, l);
+                const float4 b4 = *reinterpret_cast<const float4*>(Bt + r);
+                const float4 c4 = *reinterpret_cast<const float4*>(Ct + r);
+                s[i] = fmaf(a, s[i], bx * b4.x);
+                s[i + 1] = fmaf(a, s[i + 1], bx * b4.y);
+                s[i + 2] = fmaf(a, s[i + 2], bx * b4.z);
+                s[i + 3] = fmaf(a, s[i + 3], bx * b4.w);
+                sum = fmaf(s[i], c4.x, sum);
+                sum = fmaf(s[i + 1], c4.y, sum);
+                sum = fmaf(s[i + 2], c4.z, sum);
+                sum = fmaf(s[i + 3], c4.w, sum);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int r = ssm_row<R>(i, l);
+                s[i] = fmaf(a, s[i], bx * Bt[r]);
+                sum = fmaf(s[i], Ct[r], sum);
+            }
+        }
+        return sum;
     };
     fetch(0);
     stash(smem);
@@ -299,47 +336,33 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
         const float* Bs = buf;
         const float* Cs = buf + SSM_CHUNK * RN;
         const float* xs = Cs + SSM_CHUNK * RN;
-        const float* dts = xs + SSM_CHUNK * SSM_COLS;
+        const float* dts = xs + SSM_CHUNK * COLS;
         const float* decay = dts + SSM_CHUNK;
         if (n_tok == SSM_CHUNK) {
             float acc[SSM_CHUNK];
 #pragma unroll
-            for (int tt = 0; tt < SSM_CHUNK; ++tt) {
-                const float a = decay[tt], bx = dts[tt] * xs[tt * SSM_COLS + col_local];
-                float sum = 0.f;
+            for (int tt = 0; tt < SSM_CHUNK; ++tt)
+                acc[tt] = turn(Bs + tt * RN, Cs + tt * RN, decay[tt], dts[tt] * xs[tt * COLS + col_local]);
+            // fold: after the steps 16, 8, 4, 2 a lane holds one token's sum over 16 lanes; token = lane / 2
 #pragma unroll
-                for (int i = 0; i < R; ++i) {
-                    const int r = i * SSM_LANES + l;
-                    s[i] = fmaf(a, s[i], bx * Bs[tt * RN + r]);
-                    sum = fmaf(s[i], Cs[tt * RN + r], sum);
+            for (int half = 8, o = 16; half >= 1; half >>= 1, o >>= 1) {
+                const bool upper = (l & o) != 0;
+#pragma unroll
+                for (int k = 0; k < half; ++k) {
+                    const float send = upper ? acc[k] : acc[k + half];
+                    const float keep = upper ? acc[k + half] : acc[k];
+                    acc[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
-                acc[tt] = sum;
             }
-#pragma unroll
-            for (int tt = 0; tt < SSM_CHUNK; ++tt) {
-#pragma unroll
-                for (int o = SSM_LANES / 2; o > 0; o >>= 1)
-                    acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
-            }
-#pragma unroll
-            for (int tt = 0; tt < SSM_CHUNK; ++tt) {
-                if ((tt % SSM_LANES) == l && live)       // the lanes of a column share the chunk's stores
-                    y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xs[tt * SSM_COLS + col_local], acc[tt]);
-            }
+            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+            const int tt = l >> 1;
+            if ((l & 1) == 0 && live)
+                y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xs[tt * COLS + col_local], acc[0]);
         } else {
             for (int tt = 0; tt < n_tok; ++tt) {
-                const float xv = xs[tt * SSM_COLS + col_local];
-                const float a = decay[tt], bx = dts[tt] * xv;
-                float acc = 0.f;
-#pragma unroll
-                for (int i = 0; i < R; ++i) {
-                    const int r = i * SSM_LANES + l;
-                    s[i] = fmaf(a, s[i], bx * Bs[tt * RN + r]);
-                    acc = fmaf(s[i], Cs[tt * RN + r], acc);
-                }
-#pragma unroll
-                for (int o = SSM_LANES / 2; o > 0; o >>= 1)
-                    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                const float xv = xs[tt * COLS + col_local];
+                float acc = turn(Bs + tt * RN, Cs + tt * RN, decay[tt], dts[tt] * xv);
+                acc = warp_sum(acc);
                 if (l == 0 && live)
                     y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xv, acc);
             }
@@ -351,7 +374,7 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
     if (live) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const int r = i * SSM_LANES + l;
+            const int r = ssm_row<R>(i, l);
             if (r < N)
                 S[r] = s[i];
         }
@@ -382,6 +405,13 @@ gated_group_rms_kernel(const float* __restrict__ y, const TX* __restrict__ z, lo
 }
 
 // ---------------------------------------------------------------- dense feed-forward's gate
+__device__ __forceinline__ float clamped_swish(float g, float u, float limit, float slope)
+{
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoid_f(slope * g) * (u + 1.f);
+}
+
 template <typename TX>
 __global__ void clamped_swish_gate_kernel(const TX* __restrict__ gate_up, long long stride, TX* __restrict__ out,
                                           long long rows, int n, float limit, float slope)
@@ -392,9 +422,36 @@ __global__ void clamped_swish_gate_kernel(const TX* __restrict__ gate_up, long l
          i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / n;
         const int c = (int)(i - r * n);
-        const float g = fminf(to_f32(gate_up[r * stride + c]), limit);
-        const float u = fminf(fmaxf(to_f32(gate_up[r * stride + n + c]), -limit), limit);
-        out[i] = from_f32<TX>(g * sigmoid_f(slope * g) * (u + 1.f));
+        out[i] = from_f32<TX>(clamped_swish(to_f32(gate_up[r * stride + c]), to_f32(gate_up[r * stride + n + c]), limit,
+                                            slope));
+    }
+}
+
+// bfloat16, eight columns (16 bytes) a thread; n and the row stride are multiples of 8 and the arrays start on
+// 16-byte boundaries
+__global__ void clamped_swish_gate_wide_kernel(const __nv_bfloat16* __restrict__ gate_up, long long stride,
+                                               __nv_bfloat16* __restrict__ out, long long rows, int n, float limit,
+                                               float slope)
+{
+    pdl_enter();
+    const int per_row = n / 8;
+    const long long total = rows * per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / per_row;
+        const int c = (int)(i - r * per_row) * 8;
+        const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + r * stride + c);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + r * stride + n + c);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
+        const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+        uint4 oraw;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(gh[j]), u = __bfloat1622float2(uh[j]);
+            oh[j] = __floats2bfloat162_rn(clamped_swish(g.x, u.x, limit, slope), clamped_swish(g.y, u.y, limit, slope));
+        }
+        *reinterpret_cast<uint4*>(out + r * n + c) = oraw;
     }
 }
 
@@ -633,16 +690,19 @@ CHIBI_API int chibi_differential_combine(const float* att, const void* gate, int
     return launch_status();
 }
 
-template <typename TX, int R>
-static void launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const void* xbc, long long xbc_stride,
+template <typename TX, int R, int COLS>
+static void launch_scan(int seqs, cudaStream_t stream, const void* xbc, long long xbc_stride,
                         const void* dt_raw, long long dt_stride, const float* dt_bias, const float* a_log,
                         const float* skip, float* state, float* y, const int* q_start, const int* slots, int heads,
                         int groups, int e, int N)
 {
+    const dim3 grid((unsigned)((e + COLS - 1) / COLS), (unsigned)heads, (unsigned)seqs);
+    const size_t smem = (size_t)2 * (2 * SSM_CHUNK * R * 32 + SSM_CHUNK * COLS + 2 * SSM_CHUNK) * sizeof(float);
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(state_space_scan_kernel<TX, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    launch(state_space_scan_kernel<TX, R>, grid, dim3(SSM_THREADS), smem, stream, (const TX*)xbc, xbc_stride,
-           (const TX*)dt_raw, dt_stride, dt_bias, a_log, skip, state, y, q_start, slots, heads, groups, e, N);
+        cudaFuncSetAttribute(state_space_scan_kernel<TX, R, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    launch(state_space_scan_kernel<TX, R, COLS>, grid, dim3(32 * COLS), smem, stream, (const TX*)xbc,
+           xbc_stride, (const TX*)dt_raw, dt_stride, dt_bias, a_log, skip, state, y, q_start, slots, heads, groups, e, N);
 }
 
 CHIBI_API int chibi_state_space_scan(const void* xbc, int x_type, long long xbc_stride, const void* dt_raw,
@@ -655,23 +715,30 @@ CHIBI_API int chibi_state_space_scan(const void* xbc, int x_type, long long xbc_
     if (!xbc || !dt_raw || !dt_bias || !a_log || !skip || !state || !y || heads <= 0 || groups <= 0
         || heads % groups != 0 || e <= 0 || N <= 0)
         return CHIBI_ERR_ARGUMENT;
-    if (N > 32 * SSM_LANES || heads > 65535 || seqs > 65535)
+    if (N > 8 * 32 || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
-    const dim3 grid((unsigned)((e + SSM_COLS - 1) / SSM_COLS), (unsigned)heads, (unsigned)seqs);
-    const int rows = (N + SSM_LANES - 1) / SSM_LANES;
+    // blocks of 16 columns, or of 8 where those would leave SMs without a block
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const bool narrow = (long long)((e + 15) / 16) * heads * seqs < sms && e > 8;
+    const int rows = (N + 31) / 32;
 #define CHIBI_SCAN(RR)                                                                                       \
     CHIBI_DISPATCH_TYPE(x_type, TX, {                                                                        \
-        const size_t smem = (size_t)2 * (2 * SSM_CHUNK * RR * SSM_LANES + SSM_CHUNK * SSM_COLS + 2 * SSM_CHUNK) \
-            * sizeof(float);                                                                                 \
-        launch_scan<TX, RR>(grid, smem, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, skip,   \
-                            state, y, q_start, slots, heads, groups, e, N);                                 \
+        if (narrow)                                                                                          \
+            launch_scan<TX, RR, 8>(seqs, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, skip,  \
+                                   state, y, q_start, slots, heads, groups, e, N);                          \
+        else                                                                                                 \
+            launch_scan<TX, RR, 16>(seqs, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, skip, \
+                                    state, y, q_start, slots, heads, groups, e, N);                         \
     })
     if (rows <= 1) CHIBI_SCAN(1);
     else if (rows <= 2) CHIBI_SCAN(2);
     else if (rows <= 4) CHIBI_SCAN(4);
-    else if (rows <= 8) CHIBI_SCAN(8);
-    else if (rows <= 16) CHIBI_SCAN(16);
-    else CHIBI_SCAN(32);
+    else CHIBI_SCAN(8);
 #undef CHIBI_SCAN
     return launch_status();
 }
@@ -700,6 +767,12 @@ CHIBI_API int chibi_clamped_swish_gate(const void* gate_up, int x_type, long lon
         return CHIBI_OK;
     if (!gate_up || !out || n <= 0 || !(limit > 0.f))
         return CHIBI_ERR_ARGUMENT;
+    if (x_type == CHIBI_BF16 && n % 8 == 0 && stride % 8 == 0
+        && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        launch(clamped_swish_gate_wide_kernel, dim3(blocks_of(rows * (n / 8), 256)), dim3(256), 0, stream,
+               (const __nv_bfloat16*)gate_up, stride, (__nv_bfloat16*)out, rows, n, limit, slope);
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         launch(clamped_swish_gate_kernel<TX>, dim3(blocks_of(rows * n, 256)), dim3(256), 0, stream,
                (const TX*)gate_up, stride, (TX*)out, rows, n, limit, slope);
@@ -739,7 +812,9 @@ CHIBI_API int chibi_identity_rows(const void* x, int x_type, long long x_stride,
     const int* offsets = route;
     const int* token_of_row = route + buckets + 1 + 2 * pairs + 2 * (long long)max_tiles;
     CHIBI_DISPATCH_TYPE(x_type, TX, {
-        launch(identity_rows_kernel<TX>, dim3(blocks_of(pairs * n, 256)), dim3(256), 0, stream, (const TX*)x,
+        // (how many rows the bucket holds is known on the device only: a grid that fills the SMs, whatever it is)
+        const unsigned blocks = blocks_of(pairs * n, 256);
+        launch(identity_rows_kernel<TX>, dim3(blocks < 1184u ? blocks : 1184u), dim3(256), 0, stream, (const TX*)x,
                x_stride, offsets, token_of_row, y, n, bucket);
     });
     return launch_status();

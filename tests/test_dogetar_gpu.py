@@ -311,16 +311,17 @@ def test_gated_norm_in_parts(kernels, dtype, T, W, parts):
 
 # ------------------------------------------------------------------ feed-forwards
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_clamped_gate(kernels, dtype):
+@pytest.mark.parametrize("n", [70, 72, 1024])                  # (multiples of 8: 16 bytes of bfloat16 a thread)
+def test_clamped_gate(kernels, dtype, n):
     g = torch.Generator().manual_seed(3)
-    gu = torch.randn(33, 2 * 70, generator=g) * 2
+    gu = torch.randn(33, 2 * n, generator=g) * 2
     gd = rounded(gu, dtype)
-    a, u = gd[:, :70].clamp(max=1.25), gd[:, 70:].clamp(-1.25, 1.25)
+    a, u = gd[:, :n].clamp(max=1.25), gd[:, n:].clamp(-1.25, 1.25)
     ref = a * torch.sigmoid(1.702 * a) * (u + 1)
-    out = torch.empty(33, 70, dtype=DTYPES[dtype], device=DEV)
+    out = torch.empty(33, n, dtype=DTYPES[dtype], device=DEV)
     kernels.clamped_swish_gate(gu.to(DTYPES[dtype]).to(DEV), out, 1.25, 1.702)
     close(out, ref, KTOL[dtype], f"clamped gate {dtype}")
-    assert float(ref.max()) <= 1.25 * 2.25 and float((gd[:, :70] > 1.25).sum()) > 0 and float((gd[:, 70:] < -1.25).sum()) > 0
+    assert float(ref.max()) <= 1.25 * 2.25 and float((gd[:, :n] > 1.25).sum()) > 0 and float((gd[:, n:] < -1.25).sum()) > 0
 
 
 @pytest.mark.parametrize("n,top,groups,keep", [(8, 2, 1, 1), (8, 3, 2, 1), (8, 2, 4, 2), (20, 3, 2, 1), (6, 1, 3, 2),
