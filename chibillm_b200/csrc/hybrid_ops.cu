@@ -381,7 +381,11 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
     }
 }
 
-// grid (tokens, parts), out = v / rms(v over the part) * weight with v = y * silu(z)
+// grid (tokens, parts), out = v / rms(v over the part) * weight with v = y * silu(z).  A part of up to
+// 256 * GGR_KEEP values stays in the threads' registers between the sum of squares and the output; a longer
+// one is made a second time.
+constexpr int GGR_KEEP = 8;
+
 template <typename TX>
 __global__ void __launch_bounds__(256)
 gated_group_rms_kernel(const float* __restrict__ y, const TX* __restrict__ z, long long z_stride,
@@ -391,16 +395,36 @@ gated_group_rms_kernel(const float* __restrict__ y, const TX* __restrict__ z, lo
     __shared__ float scratch[33];
     const size_t t = blockIdx.x;
     const int c0 = blockIdx.y * part;
+    const bool kept = part <= 256 * GGR_KEEP;
+    float v[GGR_KEEP];
     float ssq = 0.f;
-    for (int c = threadIdx.x; c < part; c += blockDim.x) {
-        const float v = y[t * width + c0 + c] * silu_f(to_f32(z[t * z_stride + c0 + c]));
-        ssq = fmaf(v, v, ssq);
+    if (kept) {
+#pragma unroll
+        for (int k = 0; k < GGR_KEEP; ++k) {
+            const int c = threadIdx.x + k * 256;
+            v[k] = c < part ? y[t * width + c0 + c] * silu_f(to_f32(z[t * z_stride + c0 + c])) : 0.f;
+            ssq = fmaf(v[k], v[k], ssq);
+        }
+    } else {
+        for (int c = threadIdx.x; c < part; c += blockDim.x) {
+            const float u = y[t * width + c0 + c] * silu_f(to_f32(z[t * z_stride + c0 + c]));
+            ssq = fmaf(u, u, ssq);
+        }
     }
     ssq = block_sum(ssq, scratch);
     const float inv = 1.f / sqrtf(ssq / (float)part + eps);
+    if (kept) {
+#pragma unroll
+        for (int k = 0; k < GGR_KEEP; ++k) {
+            const int c = threadIdx.x + k * 256;
+            if (c < part)
+                out[t * width + c0 + c] = from_f32<TX>(v[k] * inv * weight[c0 + c]);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < part; c += blockDim.x) {
-        const float v = y[t * width + c0 + c] * silu_f(to_f32(z[t * z_stride + c0 + c]));
-        out[t * width + c0 + c] = from_f32<TX>(v * inv * weight[c0 + c]);
+        const float u = y[t * width + c0 + c] * silu_f(to_f32(z[t * z_stride + c0 + c]));
+        out[t * width + c0 + c] = from_f32<TX>(u * inv * weight[c0 + c]);
     }
 }
 
@@ -715,7 +739,7 @@ CHIBI_API int chibi_state_space_scan(const void* xbc, int x_type, long long xbc_
     if (!xbc || !dt_raw || !dt_bias || !a_log || !skip || !state || !y || heads <= 0 || groups <= 0
         || heads % groups != 0 || e <= 0 || N <= 0)
         return CHIBI_ERR_ARGUMENT;
-    if (N > 8 * 32 || heads > 65535 || seqs > 65535)
+    if (N > 16 * 32 || heads > 65535 || seqs > 65535)      // (two buffers of a chunk's B and C must fit shared memory)
         return CHIBI_ERR_UNSUPPORTED;
     // blocks of 16 columns, or of 8 where those would leave SMs without a block
     static int sms = 0;
@@ -738,7 +762,14 @@ CHIBI_API int chibi_state_space_scan(const void* xbc, int x_type, long long xbc_
     if (rows <= 1) CHIBI_SCAN(1);
     else if (rows <= 2) CHIBI_SCAN(2);
     else if (rows <= 4) CHIBI_SCAN(4);
-    else CHIBI_SCAN(8);
+    else if (rows <= 8) CHIBI_SCAN(8);
+    else {
+        // larger states: blocks of 8 columns only (256 threads leave a thread the registers for its rows)
+        CHIBI_DISPATCH_TYPE(x_type, TX, {
+            launch_scan<TX, 16, 8>(seqs, stream, xbc, xbc_stride, dt_raw, dt_stride, dt_bias, a_log, skip, state, y,
+                                   q_start, slots, heads, groups, e, N);
+        });
+    }
 #undef CHIBI_SCAN
     return launch_status();
 }

@@ -112,7 +112,7 @@ def test_attention_with_a_sink_and_a_linear_bias_in_blocks(kernels, dtype, H, G,
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,e,rot", [(4, 2, 8, 16, 4), (6, 2, 10, 14, 6), (4, 2, 32, 64, 32), (2, 1, 64, 128, 16),
-                                         (2, 2, 12, 12, 0)])
+                                         (2, 2, 12, 12, 0), (4, 2, 32, 32, 16), (3, 1, 16, 48, 8), (2, 2, 128, 128, 64)])
 def test_two_maps_share_their_values(kernels, dtype, H, G, d, e, rot):
     """The differential layer's attention: the maps of a key head are key heads of their own, the values are
     stored once; then the maps are joined, normalised and gated."""
@@ -215,7 +215,7 @@ def test_heads_with_biases_norms_and_rotation(kernels, dtype, H, G, d, e, rot):
 # ------------------------------------------------------------------ the state-space branch
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,e,N,G,taps", [(4, 12, 8, 2, 3), (3, 10, 5, 1, 1), (4, 64, 64, 1, 4), (6, 7, 9, 3, 5),
-                                          (2, 40, 130, 2, 2), (8, 16, 256, 4, 4)])
+                                          (2, 40, 130, 2, 2), (8, 16, 256, 4, 4), (2, 9, 300, 1, 2), (1, 20, 500, 1, 3)])
 def test_convolution_and_scan_over_portions(kernels, dtype, H, e, N, G, taps):
     """Two sequences side by side, one in portions and one token by token from a slot that was used before,
     against the plain recurrence over the whole sequences; the kept state is compared too."""
@@ -296,7 +296,7 @@ def test_a_value_survives_long_in_the_state(kernels, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,W,parts", [(1, 48, 1), (37, 30, 3), (300, 256, 2), (5, 1000, 8)])
+@pytest.mark.parametrize("T,W,parts", [(1, 48, 1), (37, 30, 3), (300, 256, 2), (5, 1000, 8), (3, 5000, 2), (2, 2048, 1)])
 def test_gated_norm_in_parts(kernels, dtype, T, W, parts):
     g = torch.Generator().manual_seed(T + W)
     y, z, w = torch.randn(T, W, generator=g) * 3, torch.randn(T, W, generator=g), 0.5 + torch.rand(W, generator=g)
