@@ -582,6 +582,31 @@ def test_a_batch_against_each_request_alone(folders, dtype):
     compare(together, ref, margins, dtype, f"dogetar G3 {dtype} together")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_whole_and_in_portions(folders, dtype):
+    """1,300 tokens through the model of tensor-core sizes: whole, in portions of 100 to 130 tokens (few query
+    rows over a long context, where the prompt kernels cut the keys into ranges) and with its last 40 tokens
+    decoded; windows, blocks and the looped layers' caches far from the sequence's start."""
+    cfg = dogetar_models.get("G3")
+    w = weights_for(cfg, "bfloat16")                 # (the corrections spaced out: 1,300 positions without a close call)
+    reqs = helpers.random_requests(cfg["vocab"], [1300], seed=31)
+    margins = {}
+    ref = dogetar_models.plain_logits(cfg, SEED, reqs, weights=w, margins=margins)
+    runner = make_runner(folders["G3", "bfloat16"], dtype, 16, 1344)
+    ids = reqs["r0"]
+    steps, pos, sizes, k = [], 0, [100, 130, 128, 3, 117], 0
+    while pos < len(ids):
+        n = min(sizes[k % len(sizes)], len(ids) - pos)
+        k += 1
+        steps.append({"step": len(steps), "entries": [{"id": "r0", "tokens": ids[pos:pos + n], "want": list(range(n))}],
+                      "end": ["r0"] if pos + n == len(ids) else []})
+        pos += n
+    for trace, what in ((helpers.trace_whole(reqs), "whole"), (steps, "portions of about 100"),
+                        (helpers.trace_last_decoded(reqs, 40), "last 40 decoded")):
+        compare(helpers.run_trace(runner, trace), ref, margins, dtype, f"dogetar G3 {dtype} long prompt {what}")
+    runner.runtime.kernels.check_error_word()
+
+
 def test_long_decoding(folders):
     """Three tokens of prompt, then 300 tokens one by one (captured steps replayed): blocks of 24 and 20
     positions and a window of 13 pass over decoded tokens many times, the state-space branch's state is
