@@ -202,17 +202,20 @@ differential_combine_kernel(const float* __restrict__ att, const TX* __restrict_
 }
 
 // ---------------------------------------------------------------- state-space scan
-// grid (blocks of COLS value columns, heads, sequences); a warp owns a value column, lane l of it with R of
-// the column's state rows in registers from the sequence's first token of the step to its last.  The state
-// is kept value column first: [slots, heads, e, N], so that a warp's rows are one contiguous run.  Tokens
-// come in chunks of SSM_CHUNK through two buffers in shared memory (B and C of the head's group, rows padded
-// with zeros to 32 R; the block's x columns; the step sizes and decays): the next chunk's loads are issued
-// before the present chunk's arithmetic and stored after it, one block barrier a chunk.  In a full chunk
-// the 16 sums over the lanes are folded together after the chunk's last token (at every step of the
-// butterfly a lane passes on the half of its sums that its partner keeps: 16 exchanges for 16 tokens instead
-// of 80), and lane 2 t ends with token t's sum.  A token's turn is then 2 R multiply-adds a lane and nothing
-// that waits for another lane; the many warps of a block hide the shared-memory loads of one another.
+// grid (blocks of COLS value columns, heads, sequences); a warp owns two neighbouring value columns, lane l
+// of it with R of each column's state rows in registers from the sequence's first token of the step to its
+// last (a token's B and C rows, which all columns share, are fetched from shared memory once for the two).
+// The state is kept value column first: [slots, heads, e, N], so that a column's rows are one contiguous run.
+// Tokens come in chunks of SSM_CHUNK through two buffers in shared memory (B and C of the head's group, rows
+// padded with zeros to 32 R; the block's x columns; the step sizes and decays): the next chunk's loads are
+// issued before the present chunk's arithmetic and stored after it, one block barrier a chunk.  In a full
+// chunk the 32 sums over the lanes (16 tokens x 2 columns) are folded together after the chunk's last token:
+// at every step of the butterfly a lane passes on the half of its sums that its partner keeps, 31 exchanges
+// instead of 160, and lane l ends with the sum of token l / 2, column l % 2.  A token's turn is then 2 R
+// multiply-adds a lane and column and nothing that waits for another lane; the warps of a block hide the
+// shared-memory loads of one another.
 constexpr int SSM_CHUNK = 16;
+constexpr int SSM_CW = 2;                               // columns of a warp
 
 // The state row that lane l holds as its i-th: runs of four rows to a lane where a lane has four or more
 // (one 16-byte load of B and of C serves four multiply-adds), else row 32 i + l.
@@ -221,9 +224,9 @@ template <int R> __device__ __forceinline__ int ssm_row(int i, int l)
     return R >= 4 ? (i >> 2) * 128 + l * 4 + (i & 3) : i * 32 + l;
 }
 
-// COLS: value columns (warps) of a block: 16, or 8 where 16 would leave SMs without a block.
+// COLS: value columns of a block: 16, or 8 where 16 would leave SMs without a block.
 template <typename TX, int R, int COLS>
-__global__ void __launch_bounds__(32 * COLS)
+__global__ void __launch_bounds__(32 * COLS / SSM_CW)
 state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const TX* __restrict__ dt_raw,
                         long long dt_stride, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                         const float* __restrict__ skip, float* state, float* __restrict__ y,
@@ -231,29 +234,31 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
                         int N)
 {
     pdl_enter();
-    constexpr int THREADS = 32 * COLS;
+    constexpr int THREADS = 32 * COLS / SSM_CW;
     constexpr int RN = 32 * R;                          // padded rows of a token's B and C
     constexpr int PER = SSM_CHUNK * RN / THREADS;       // values of B (and of C) that a thread fetches a chunk
     constexpr int BUF = 2 * SSM_CHUNK * RN + SSM_CHUNK * COLS + 2 * SSM_CHUNK;
-    static_assert(SSM_CHUNK * RN % THREADS == 0 && SSM_CHUNK * COLS <= THREADS && BUF % 4 == 0 && SSM_CHUNK == 16,
-                  "a chunk's values divide evenly among the threads");
+    static_assert(SSM_CHUNK * RN % THREADS == 0 && SSM_CHUNK * COLS <= THREADS && BUF % 4 == 0 && SSM_CHUNK == 16
+                  && SSM_CW == 2, "a chunk's values divide evenly among the threads");
     extern __shared__ __align__(16) float smem[];
     const int h = blockIdx.y, seq = blockIdx.z;
     const int g = h / (heads / groups);
     const int inner = heads * e;
-    const int col_local = threadIdx.x >> 5, l = threadIdx.x & 31;
-    const int col = blockIdx.x * COLS + col_local;
-    const bool live = col < e;
+    const int col_local = (threadIdx.x >> 5) * SSM_CW, l = threadIdx.x & 31;
+    const int col = blockIdx.x * COLS + col_local;      // the warp's first column
     const int row0 = q_start[seq];
     const int q_len = q_start[seq + 1] - row0;
     if (q_len <= 0)
         return;
-    float* S = state + (((size_t)slots[seq] * heads + h) * e + (live ? col : 0)) * N;
-    float s[R];
+    float* S = state + (((size_t)slots[seq] * heads + h) * e) * N;
+    float s[SSM_CW][R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int r = ssm_row<R>(i, l);
-        s[i] = (live && r < N) ? S[r] : 0.f;
+    for (int w = 0; w < SSM_CW; ++w) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int r = ssm_row<R>(i, l);
+            s[w][i] = (col + w < e && r < N) ? S[(size_t)(col + w) * N + r] : 0.f;
+        }
     }
     const float A = -expf(a_log[h]), bias = dt_bias[h], D = skip[h];
 
@@ -295,33 +300,35 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
             buf[2 * SSM_CHUNK * RN + SSM_CHUNK * COLS + SSM_CHUNK + threadIdx.x] = expf(A * dt);
         }
     };
-    // one token's turn on this lane's rows: the state's update and the rows' part of S^T C
-    auto turn = [&](const float* Bt, const float* Ct, float a, float bx) {
-        float sum = 0.f;
+    // one token's turn on this lane's rows of both columns: the state's update and the rows' part of S^T C
+    auto turn = [&](const float* Bt, const float* Ct, float a, float bx0, float bx1, float& sum0, float& sum1) {
+        sum0 = sum1 = 0.f;
         if constexpr (R >= 4) {
 #pragma unroll
             for (int i = 0; i < R; i += 4) {
                 const int r = ssm_row<R>(i, l);
                 const float4 b4 = *reinterpret_cast<const float4*>(Bt + r);
                 const float4 c4 = *reinterpret_cast<const float4*>(Ct + r);
-                s[i] = fmaf(a, s[i], bx * b4.x);
-                s[i + 1] = fmaf(a, s[i + 1], bx * b4.y);
-                s[i + 2] = fmaf(a, s[i + 2], bx * b4.z);
-                s[i + 3] = fmaf(a, s[i + 3], bx * b4.w);
-                sum = fmaf(s[i], c4.x, sum);
-                sum = fmaf(s[i + 1], c4.y, sum);
-                sum = fmaf(s[i + 2], c4.z, sum);
-                sum = fmaf(s[i + 3], c4.w, sum);
+                const float bv[4] = { b4.x, b4.y, b4.z, b4.w }, cv[4] = { c4.x, c4.y, c4.z, c4.w };
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    s[0][i + j] = fmaf(a, s[0][i + j], bx0 * bv[j]);
+                    s[1][i + j] = fmaf(a, s[1][i + j], bx1 * bv[j]);
+                    sum0 = fmaf(s[0][i + j], cv[j], sum0);
+                    sum1 = fmaf(s[1][i + j], cv[j], sum1);
+                }
             }
         } else {
 #pragma unroll
             for (int i = 0; i < R; ++i) {
                 const int r = ssm_row<R>(i, l);
-                s[i] = fmaf(a, s[i], bx * Bt[r]);
-                sum = fmaf(s[i], Ct[r], sum);
+                const float bv = Bt[r], cv = Ct[r];
+                s[0][i] = fmaf(a, s[0][i], bx0 * bv);
+                s[1][i] = fmaf(a, s[1][i], bx1 * bv);
+                sum0 = fmaf(s[0][i], cv, sum0);
+                sum1 = fmaf(s[1][i], cv, sum1);
             }
         }
-        return sum;
     };
     fetch(0);
     stash(smem);
@@ -339,13 +346,14 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
         const float* dts = xs + SSM_CHUNK * COLS;
         const float* decay = dts + SSM_CHUNK;
         if (n_tok == SSM_CHUNK) {
-            float acc[SSM_CHUNK];
+            float acc[SSM_CHUNK * SSM_CW];              // [token][column of the warp]
 #pragma unroll
             for (int tt = 0; tt < SSM_CHUNK; ++tt)
-                acc[tt] = turn(Bs + tt * RN, Cs + tt * RN, decay[tt], dts[tt] * xs[tt * COLS + col_local]);
-            // fold: after the steps 16, 8, 4, 2 a lane holds one token's sum over 16 lanes; token = lane / 2
+                turn(Bs + tt * RN, Cs + tt * RN, decay[tt], dts[tt] * xs[tt * COLS + col_local],
+                     dts[tt] * xs[tt * COLS + col_local + 1], acc[2 * tt], acc[2 * tt + 1]);
+            // fold: after the steps 16, 8, 4, 2, 1 lane l holds the sum over all lanes of value l
 #pragma unroll
-            for (int half = 8, o = 16; half >= 1; half >>= 1, o >>= 1) {
+            for (int half = SSM_CHUNK * SSM_CW / 2, o = 16; half >= 1; half >>= 1, o >>= 1) {
                 const bool upper = (l & o) != 0;
 #pragma unroll
                 for (int k = 0; k < half; ++k) {
@@ -354,29 +362,31 @@ state_space_scan_kernel(const TX* __restrict__ xbc, long long xbc_stride, const 
                     acc[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
             }
-            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
-            const int tt = l >> 1;
-            if ((l & 1) == 0 && live)
-                y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xs[tt * COLS + col_local], acc[0]);
+            const int tt = l >> 1, w = l & 1;
+            if (col + w < e)
+                y[(size_t)(row0 + c0 + tt) * inner + h * e + col + w] = fmaf(D, xs[tt * COLS + col_local + w], acc[0]);
         } else {
             for (int tt = 0; tt < n_tok; ++tt) {
-                const float xv = xs[tt * COLS + col_local];
-                float acc = turn(Bs + tt * RN, Cs + tt * RN, decay[tt], dts[tt] * xv);
-                acc = warp_sum(acc);
-                if (l == 0 && live)
-                    y[(size_t)(row0 + c0 + tt) * inner + h * e + col] = fmaf(D, xv, acc);
+                const float xv0 = xs[tt * COLS + col_local], xv1 = xs[tt * COLS + col_local + 1];
+                float a0, a1;
+                turn(Bs + tt * RN, Cs + tt * RN, decay[tt], dts[tt] * xv0, dts[tt] * xv1, a0, a1);
+                a0 = warp_sum(a0);
+                a1 = warp_sum(a1);
+                if (l < SSM_CW && col + l < e)
+                    y[(size_t)(row0 + c0 + tt) * inner + h * e + col + l] = l ? fmaf(D, xv1, a1) : fmaf(D, xv0, a0);
             }
         }
         if (more)
             stash(smem + (which ^ 1) * BUF);
         __syncthreads();
     }
-    if (live) {
+#pragma unroll
+    for (int w = 0; w < SSM_CW; ++w) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int r = ssm_row<R>(i, l);
-            if (r < N)
-                S[r] = s[i];
+            if (col + w < e && r < N)
+                S[(size_t)(col + w) * N + r] = s[w][i];
         }
     }
 }
@@ -725,7 +735,7 @@ static void launch_scan(int seqs, cudaStream_t stream, const void* xbc, long lon
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(state_space_scan_kernel<TX, R, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);
-    launch(state_space_scan_kernel<TX, R, COLS>, grid, dim3(32 * COLS), smem, stream, (const TX*)xbc,
+    launch(state_space_scan_kernel<TX, R, COLS>, grid, dim3(32 * COLS / SSM_CW), smem, stream, (const TX*)xbc,
            xbc_stride, (const TX*)dt_raw, dt_stride, dt_bias, a_log, skip, state, y, q_start, slots, heads, groups, e, N);
 }
 
