@@ -355,7 +355,7 @@ def test_router_ties_go_to_the_lower_number(kernels):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,D,F,E,identity,top", [(1, 64, 24, 6, 2, 2), (9, 48, 16, 4, 2, 1), (300, 96, 40, 5, 3, 4),
-                                                  (700, 128, 64, 7, 1, 2), (64, 256, 128, 8, 0, 2), (5, 320, 96, 16, 4, 3),
+                                                  (700, 128, 64, 7, 1, 2), (64, 256, 128, 8, 0, 2), (5, 352, 160, 12, 2, 3),
                                                   (1500, 256, 64, 3, 1, 2), (40, 72, 24, 5, 3, 4)])
 def test_gated_experts_with_identity_ones(kernels, dtype, T, D, F, E, identity, top):
     """Choices given (every output appears, identity ones too): the sum over a token's choices of weight *
